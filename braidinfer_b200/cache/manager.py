@@ -1,8 +1,9 @@
 """The cache on the device: keys and values per layer group, a fixed-size state area
 per sequence, and the per-step page tables that kernels read.
 
-Storage of a group: [layer_in_group][page][2 (K, V)][kv_head][page_size][head_dim] in
-the run's element type.  A group collects the schedule entries whose mixers asked for
+Storage of a group: [layer_in_group][page][planes][kv_head][page_size][head_dim] in
+the run's element type; planes is 2 (K, V), or 1 where a mixer keeps one vector a token
+that is key and value at once (`CacheRequest.planes`).  A group collects the schedule entries whose mixers asked for
 the same thing (`CacheRequest.group_key`): all keys, or a window of them.  The
 reference's layout is one 64-token chunk holding all layers
 (crates/braidinfer-runtime/src/paged_kv.rs:17-21); per-layer pools make a layer's pages
@@ -26,7 +27,7 @@ PAGE_SIZE = _page_size()      # csrc/page.h holds the number
 @dataclass
 class LayerCache:
     """What a mixer sees of the cache during one step."""
-    storage: torch.Tensor            # [pages, 2, kv_heads, page_size, head_dim]
+    storage: torch.Tensor            # [pages, planes, kv_heads, page_size, head_dim]
     page_size: int
     read_only: bool
     group: int
@@ -38,7 +39,7 @@ class CacheGroup:
         self.request = request
         self.entries = entries                   # schedule entries that own a layer here
         self.pages = GroupPages(num_pages, PAGE_SIZE, request.kind, request.window)
-        self.storage = torch.zeros((len(entries), num_pages, 2, request.num_kv_heads, PAGE_SIZE, request.head_dim),
+        self.storage = torch.zeros((len(entries), num_pages, request.planes, request.num_kv_heads, PAGE_SIZE, request.head_dim),
                                    dtype=dtype, device=device)
 
     def nbytes(self) -> int:
@@ -101,7 +102,7 @@ class CacheManager:
         sees (a windowed owner gives pages back once its own window has passed them)."""
         if reader is None:
             return                            # a mixer that keeps nothing ignores the view it is handed
-        if (reader.num_kv_heads, reader.head_dim) != (owner.num_kv_heads, owner.head_dim):
+        if (reader.num_kv_heads, reader.head_dim, reader.planes) != (owner.num_kv_heads, owner.head_dim, owner.planes):
             raise CacheError(
                 f"schedule entry {e} reads the cache of entry {owner_entry}, but its mixer expects "
                 f"{reader.num_kv_heads} kv heads of {reader.head_dim} and that cache holds "

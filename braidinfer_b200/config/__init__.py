@@ -1,6 +1,7 @@
 """Typed configurations read from config.json."""
 from .errors import ConfigError, UnknownArchitectureError
 from .mistral import MistralConfig
+from .bidinex import BidinexConfig
 from .presets import PRESETS, preset
 
 

@@ -114,6 +114,7 @@ class Kernels:
         self._error_flag = torch.zeros(8, dtype=torch.int32, device="cuda")
         self._tc_workspace: Optional[torch.Tensor] = None
         self._attn_libs = {}
+        self._part_libs = {}
         self.pending_partial = None     # the open PartialProduct, if any (it owns the GEMM workspace)
         self.workspace_generation = 0   # grows when a scratch buffer moves (captured graphs are stale then)
         self._attn_partial: Optional[torch.Tensor] = None
@@ -123,7 +124,7 @@ class Kernels:
     def _declare(self) -> None:
         L = self.lib
         L.braid_last_error.restype = c_char_p
-        L.braid_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        L.braid_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
         L.braid_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
         L.braid_silu_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         L.braid_residual_add.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
@@ -158,6 +159,12 @@ class Kernels:
         L.braid_argmax.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p]
         L.braid_sample.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int] + [c_void_p] * 12 + \
                                   [c_void_p, c_void_p]
+        L.braid_dyt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                                c_float, c_void_p]
+        L.braid_softcap.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
+        L.braid_concat2.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        for name in ("braid_dyt", "braid_softcap", "braid_concat2"):
+            getattr(L, name).restype = c_int
         for name in ("braid_embed", "braid_rmsnorm", "braid_silu_mul", "braid_residual_add",
                      "braid_rope_kv_write", "braid_cast", "braid_attn_simple", "braid_gemm_simt",
                      "braid_gemm_tc", "braid_gemm_tc2", "braid_argmax", "braid_sample", "braid_streamk_reduce",
@@ -206,11 +213,12 @@ class Kernels:
                                               self._stream()), "logit_hash")
         return [v & 0xFFFFFFFFFFFFFFFF for v in out[:n].tolist()]
 
-    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+        """out[t] = table[ids[t]] * scale, float32."""
         n, hidden = out.shape
         self.launches += 1
         self._check(self.lib.braid_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
-                                         n, hidden, table.shape[0], self._stream()), "embed")
+                                         n, hidden, table.shape[0], float(scale), self._stream()), "embed")
 
     def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float,
                 row_index: Optional[torch.Tensor] = None) -> None:
@@ -352,6 +360,204 @@ class Kernels:
                                 1 if few_tokens else 0, float(scale), self._error_flag.data_ptr() + 16, self._stream())
         if rc != 0:
             raise KernelError(f"attn_mma: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
+
+    # ------------------------------------------------------------------ element-wise kernels of other models
+    def dyt(self, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor, out: torch.Tensor,
+            row_index: Optional[torch.Tensor] = None, in_scale: float = 1.0) -> None:
+        """Dynamic Tanh: out = tanh(alpha * (x * in_scale)) * w + b, x the float32 residual stream (out may be x)."""
+        rows, width = out.shape
+        if x.dtype != torch.float32:
+            raise KernelError("dyt reads the float32 residual stream")
+        if not (w.dtype == b.dtype == alpha.dtype):
+            raise KernelError("dyt: weight, bias and alpha must have one element type")
+        self.launches += 1
+        self._check(self.lib.braid_dyt(x.data_ptr(), w.data_ptr(), b.data_ptr(), alpha.data_ptr(), dtype_code(w.dtype),
+                                       out.data_ptr(), dtype_code(out.dtype), _ptr(row_index), rows, width,
+                                       float(in_scale), self._stream()), "dyt")
+
+    def softcap(self, logits: torch.Tensor, cap: float) -> None:
+        """logits <- cap * tanh(logits / cap), in place (float32, contiguous)."""
+        if logits.dtype != torch.float32 or not logits.is_contiguous():
+            raise KernelError("softcap works in place on contiguous float32 logits")
+        self.launches += 1
+        self._check(self.lib.braid_softcap(logits.data_ptr(), logits.numel(), float(cap), self._stream()), "softcap")
+
+    def concat2(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+        """out[r] = [a[r], b[r]]: two float32 streams side by side, in out's element type."""
+        rows, width = a.shape
+        if a.dtype != torch.float32 or b.dtype != torch.float32 or b.shape != a.shape or tuple(out.shape) != (rows, 2 * width):
+            raise KernelError("concat2 wants two float32 tensors of one shape and an output twice as wide")
+        self.launches += 1
+        self._check(self.lib.braid_concat2(a.data_ptr(), b.data_ptr(), out.data_ptr(), dtype_code(out.dtype), rows, width,
+                                           self._stream()), "concat2")
+
+    # ------------------------------------------------------------------ libraries of single kinds of parts
+    def part_library(self, name: str):
+        """The kernel library of one kind of part ("latent", "moe"), compiled and opened at first use."""
+        lib = self._part_libs.get(name)
+        if lib is None:
+            lib = ctypes.CDLL(str(build.part_library(name, verbose=self._verbose)))
+            lib.braid_last_error.restype = c_char_p
+            if name == "latent":
+                lib.braid_latent_prep.argtypes = [c_void_p, c_longlong, c_int] + [c_void_p] * 7 + [c_int] * 10 + \
+                                                 [c_float, c_void_p, c_void_p]
+                lib.braid_gemm_heads.argtypes = [c_void_p] * 4 + [c_int] * 5 + [c_longlong] * 5 + [c_float, c_void_p]
+                lib.braid_attn_latent_simple.argtypes = [c_void_p, c_void_p, c_int] + [c_void_p] * 4 + \
+                                                        [c_longlong, c_longlong] + [c_int] * 8 + [c_float, c_void_p, c_void_p]
+                names = ("braid_latent_prep", "braid_gemm_heads", "braid_attn_latent_simple")
+            elif name == "moe":
+                lib.braid_moe_route.argtypes = [c_void_p] * 3 + [c_int] * 5 + [c_float, c_void_p]
+                lib.braid_moe_plan.argtypes = [c_void_p] * 6 + [c_int] * 5 + [c_void_p]
+                lib.braid_moe_gemm_simt.argtypes = [c_void_p] * 7 + [c_int, c_int, c_longlong, c_longlong] + [c_int] * 5 + \
+                                                   [c_void_p]
+                lib.braid_moe_combine.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                  c_longlong, c_void_p]
+                names = ("braid_moe_route", "braid_moe_plan", "braid_moe_gemm_simt", "braid_moe_combine")
+            else:
+                names = ()
+            for n in names:
+                getattr(lib, n).restype = c_int
+            self._part_libs[name] = lib
+        return lib
+
+    @staticmethod
+    def _check_lib(lib, rc: int, what: str) -> None:
+        if rc != 0:
+            raise KernelError(f"{what}: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
+
+    # ------------------------------------------------------------------ latent attention
+    def latent_prep(self, proj: torch.Tensor, q_cols: int, norm_w: torch.Tensor, inv_freq: torch.Tensor,
+                    positions: torch.Tensor, token_seq: torch.Tensor, page_table: Optional[torch.Tensor],
+                    cache: Optional[torch.Tensor], q_lat: torch.Tensor, heads: int, dim: int, rot: int, rank: int,
+                    rot_dims: int, page_size: int, eps: float) -> None:
+        """A step's projected rows [rows, heads*(dim+rot) + rank + rot (+ more)]: the latent part is RMS-normed and,
+        with the rotated shared key part, written into `cache` ([pages, 1, 1, page_size, rank + rot]); the rotated
+        parts of the queries are written into q_lat[:, :, rank:] ([rows, heads, rank + rot])."""
+        lib = self.part_library("latent")
+        if norm_w.dtype != proj.dtype or q_lat.dtype != proj.dtype or (cache is not None and cache.dtype != proj.dtype):
+            raise KernelError("latent_prep: rows, norm weight, queries and cache must have one element type")
+        if not q_lat.is_contiguous() or tuple(q_lat.shape) != (proj.shape[0], heads, rank + rot):
+            raise KernelError(f"latent_prep: q_lat must be contiguous [{proj.shape[0]}, {heads}, {rank + rot}]")
+        if cache is not None and (cache.dim() != 5 or cache.shape[1] != 1 or cache.shape[2] != 1 or cache.shape[3] != page_size
+                                  or cache.shape[4] != rank + rot):
+            raise KernelError(f"latent_prep: the cache must be [pages, 1, 1, {page_size}, {rank + rot}], got {tuple(cache.shape)}")
+        cols = page_table.shape[1] if page_table is not None else 0
+        self.launches += 1
+        self._check_lib(lib, lib.braid_latent_prep(
+            proj.data_ptr(), proj.stride(0), q_cols, norm_w.data_ptr(), inv_freq.data_ptr(), positions.data_ptr(),
+            token_seq.data_ptr(), _ptr(page_table), _ptr(cache), q_lat.data_ptr(), dtype_code(proj.dtype),
+            proj.shape[0], heads, dim, rot, rank, rot_dims, page_size, cols, cache.shape[0] if cache is not None else 0,
+            float(eps), self._error_flag.data_ptr(), self._stream()), "latent_prep")
+
+    def gemm_heads(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                   mult: float = 1.0) -> None:
+        """out[n, h, :] = w[h] x[n, h, :] for every head: x [rows, heads, K] and out [rows, heads, J] may be views
+        (last dimension contiguous), w [heads, J, K] contiguous.  `gate` [rows, heads] (a view is fine): the result is
+        multiplied by mult * sigmoid(gate)."""
+        lib = self.part_library("latent")
+        rows, heads, k = x.shape
+        if w.dim() != 3 or w.shape[0] != heads or w.shape[2] != k or not w.is_contiguous():
+            raise KernelError(f"gemm_heads: w must be contiguous [{heads}, J, {k}], got {tuple(w.shape)}")
+        j = w.shape[1]
+        if tuple(out.shape) != (rows, heads, j) or x.stride(2) != 1 or out.stride(2) != 1:
+            raise KernelError("gemm_heads: shapes do not fit or last dimensions are not contiguous")
+        if not (x.dtype == w.dtype == out.dtype) or (gate is not None and gate.dtype != x.dtype):
+            raise KernelError("gemm_heads: every operand must have one element type")
+        if gate is not None and (tuple(gate.shape) != (rows, heads) or gate.stride(1) != 1):
+            raise KernelError("gemm_heads: gate must be [rows, heads] with contiguous heads")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_gemm_heads(
+            x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(gate), dtype_code(x.dtype), rows, heads, j, k,
+            x.stride(0), x.stride(1), out.stride(0), out.stride(1), gate.stride(0) if gate is not None else 0,
+            float(mult), self._stream()), "gemm_heads")
+
+    def attn_latent_simple(self, q_lat: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
+                           positions: torch.Tensor, token_seq: torch.Tensor, rank: int, window: Optional[int],
+                           scale: float) -> None:
+        """Multi-query attention over the latent cache, one warp per (token, head): q_lat [rows, heads, D],
+        out [rows, heads, rank], cache [pages, 1, 1, page_size, D]; a cached row is the key, its first `rank`
+        numbers the value."""
+        lib = self.part_library("latent")
+        rows, heads, d = q_lat.shape
+        if not q_lat.is_contiguous() or not out.is_contiguous() or tuple(out.shape) != (rows, heads, rank):
+            raise KernelError("attn_latent_simple: q_lat [rows, heads, D] and out [rows, heads, rank] must be contiguous")
+        if cache.dim() != 5 or cache.shape[1] != 1 or cache.shape[2] != 1 or cache.shape[4] != d or cache.dtype != q_lat.dtype:
+            raise KernelError(f"attn_latent_simple: the cache must be [pages, 1, 1, page_size, {d}] of the queries' type")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_attn_latent_simple(
+            q_lat.data_ptr(), out.data_ptr(), dtype_code(out.dtype), cache.data_ptr(), page_table.data_ptr(),
+            positions.data_ptr(), token_seq.data_ptr(), q_lat.stride(0), out.stride(0), rows, heads, d, rank,
+            cache.shape[3], page_table.shape[1], cache.shape[0], int(window or 0), float(scale),
+            self._error_flag.data_ptr() + 16, self._stream()), "attn_latent_simple")
+
+    # ------------------------------------------------------------------ mixture of experts
+    def moe_route(self, logits: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, groups: int, keep: int,
+                  mult: float = 1.0) -> None:
+        """Router logits [rows, experts] (float32) -> for each row its `top` experts idx [rows, top] (int32, by falling
+        score) and their weights wgt [rows, top] (float32): softmax scores of the chosen, over their sum, times mult."""
+        lib = self.part_library("moe")
+        rows, experts = logits.shape
+        top = idx.shape[1]
+        if logits.dtype != torch.float32 or not logits.is_contiguous() or idx.dtype != torch.int32 or wgt.dtype != torch.float32 \
+                or tuple(idx.shape) != (rows, top) or tuple(wgt.shape) != (rows, top) or not idx.is_contiguous() or not wgt.is_contiguous():
+            raise KernelError("moe_route: logits float32 [rows, experts], idx int32 and wgt float32 [rows, top], contiguous")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_moe_route(logits.data_ptr(), idx.data_ptr(), wgt.data_ptr(), rows, experts, top,
+                                                 groups, keep, float(mult), self._stream()), "moe_route")
+
+    @staticmethod
+    def moe_max_tiles(rows: int, top: int, experts: int, tile: int) -> int:
+        """An upper bound of the tiles a step's plan uses: every tile holds a pair, and every expert wastes
+        less than a tile."""
+        pairs = rows * top
+        return max(1, min(pairs, (pairs + min(experts, pairs) * (tile - 1)) // tile))
+
+    def moe_plan(self, idx: torch.Tensor, token_seq: torch.Tensor, experts: int, tile: int):
+        """Sort the (row, choice) pairs by expert, every expert's run padded to a multiple of `tile` slots.
+        Returns (slot_pair [max_tiles*tile], pair_slot [rows*top], tile_expert [max_tiles], meta [1], max_tiles)."""
+        lib = self.part_library("moe")
+        rows, top = idx.shape
+        max_tiles = self.moe_max_tiles(rows, top, experts, tile)
+        buf = torch.empty(max_tiles * tile + rows * top + max_tiles + 4, dtype=torch.int32, device=idx.device)
+        slot_pair = buf[:max_tiles * tile]
+        pair_slot = buf[max_tiles * tile:max_tiles * tile + rows * top]
+        tile_expert = buf[max_tiles * tile + rows * top:max_tiles * tile + rows * top + max_tiles]
+        meta = buf[max_tiles * tile + rows * top + max_tiles:]
+        self.launches += 1
+        self._check_lib(lib, lib.braid_moe_plan(idx.data_ptr(), token_seq.data_ptr(), slot_pair.data_ptr(),
+                                                pair_slot.data_ptr(), tile_expert.data_ptr(), meta.data_ptr(), rows, top,
+                                                experts, tile, max_tiles, self._stream()), "moe_plan")
+        return slot_pair, pair_slot, tile_expert, meta, max_tiles
+
+    def moe_gemm_simt(self, x: torch.Tensor, w0: torch.Tensor, w1: Optional[torch.Tensor], out: torch.Tensor, plan,
+                      top: int, tile: int) -> None:
+        """The experts' products over a plan's slots, plain.  With w1: out[slot] = silu(w0[e] x[row]) * (w1[e] x[row]),
+        x the step's rows; without: out[slot] = w0[e] x[slot], x a tensor of slots.  w0, w1 [experts, J, K]."""
+        lib = self.part_library("moe")
+        slot_pair, _pair_slot, tile_expert, meta, max_tiles = plan
+        j, k = w0.shape[1], w0.shape[2]
+        if not w0.is_contiguous() or (w1 is not None and (not w1.is_contiguous() or w1.shape != w0.shape)):
+            raise KernelError("moe_gemm: expert weights must be contiguous [experts, J, K]")
+        if x.shape[1] != k or out.shape[1] != j or out.shape[0] != max_tiles * tile or x.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("moe_gemm: shapes do not fit")
+        if not (x.dtype == w0.dtype == out.dtype):
+            raise KernelError("moe_gemm: every operand must have one element type")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_moe_gemm_simt(
+            x.data_ptr(), w0.data_ptr(), _ptr(w1), out.data_ptr(), slot_pair.data_ptr(), tile_expert.data_ptr(),
+            meta.data_ptr(), dtype_code(x.dtype), 0 if w1 is not None else 1, x.stride(0), out.stride(0), j, k, top, tile,
+            max_tiles, self._stream()), "moe_gemm_simt")
+
+    def moe_combine(self, h: torch.Tensor, y: torch.Tensor, plan, wgt: torch.Tensor) -> None:
+        """h[row] += sum_k wgt[row, k] * y[slot of (row, k)], float32, choices added in their order."""
+        lib = self.part_library("moe")
+        rows, width = h.shape
+        if h.dtype != torch.float32 or not h.is_contiguous() or y.shape[1] != width or y.stride(1) != 1:
+            raise KernelError("moe_combine: h is the contiguous float32 residual stream, y [slots, width]")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_moe_combine(h.data_ptr(), y.data_ptr(), dtype_code(y.dtype), plan[1].data_ptr(),
+                                                   wgt.data_ptr(), rows, width, wgt.shape[1], y.stride(0), self._stream()),
+                        "moe_combine")
 
     # ------------------------------------------------------------------ matrix products
     def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> None:

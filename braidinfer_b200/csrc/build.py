@@ -28,8 +28,10 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
 # Sources that do not depend on a model size.
-CORE_SOURCES = ["errors.cu", "elementwise.cu", "attn_simple.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_tc2.cu",
+CORE_SOURCES = ["errors.cu", "elementwise.cu", "pointwise.cu", "attn_simple.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_tc2.cu",
                 "fused_reduce.cu", "sampling.cu"]
+# Kernels that only some models use: each a library of its own, compiled when a model that needs it is built.
+PART_SOURCES = {"latent": ["errors.cu", "latent.cu"], "moe": ["errors.cu", "moe.cu"]}
 HEADERS = ["common.cuh", "rowscale.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h", "page.h", "trace.cuh"]
 
 
@@ -162,6 +164,13 @@ def core_library(verbose: bool = True) -> Path:
     if trace_build():
         return build_library("braidinfer_core_trace", CORE_SOURCES, defines=["-DBRAID_TRACE"], verbose=verbose)
     return build_library("braidinfer_core", CORE_SOURCES, verbose=verbose)
+
+
+def part_library(name: str, verbose: bool = True) -> Path:
+    """The kernels of one kind of part ("latent": latent attention, "moe": mixture of experts)."""
+    if name not in PART_SOURCES:
+        raise BuildError(f"no kernel library named {name!r}; known: {sorted(PART_SOURCES)}")
+    return build_library(f"braidinfer_{name}", PART_SOURCES[name], verbose=verbose)
 
 
 def attention_library(head_dim: int, verbose: bool = True) -> Path:

@@ -2,7 +2,7 @@
 // with the write of keys and values into the paged cache.
 //
 // Formulas follow the reference ops they replace (by that project's paths):
-//   embedding      kernels/megakernel_ops.hip:1757-1768
+//   embedding      kernels/megakernel_ops.hip:1757-1768 (a model's constant factor on the rows is applied here; 1 there)
 //   rmsnorm        kernels/megakernel_ops.hip:862-904
 //   silu * up      kernels/megakernel_ops.hip:374-407
 //   residual add   kernels/megakernel_ops.hip:1185-1212
@@ -15,7 +15,7 @@
 // ------------------------------------------------------------------ embedding
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int n_tokens, int hidden, int vocab) {
+                             float* __restrict__ out, int n_tokens, int hidden, int vocab, float scale) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -32,23 +32,23 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
             *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(row + g * VEC);
 #pragma unroll
             for (int e = 0; e < VEC; e += 4)
-                *reinterpret_cast<float4*>(o + g * VEC + e) = make_float4(to_f32(v[e]), to_f32(v[e + 1]), to_f32(v[e + 2]), to_f32(v[e + 3]));
+                *reinterpret_cast<float4*>(o + g * VEC + e) = make_float4(to_f32(v[e]) * scale, to_f32(v[e + 1]) * scale, to_f32(v[e + 2]) * scale, to_f32(v[e + 3]) * scale);
         }
         return;
     }
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = valid ? to_f32(row[i]) : 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = valid ? to_f32(row[i]) * scale : 0.f;
 }
 
 extern "C" int braid_embed(const void* table, int table_dtype, const int* ids, float* out,
-                           int n_tokens, int hidden, int vocab, void* stream) {
+                           int n_tokens, int hidden, int vocab, float scale, void* stream) {
     if (n_tokens <= 0) return BRAID_OK;
     if (hidden <= 0 || vocab <= 0) BRAID_REFUSE("embed: hidden=%d vocab=%d must be positive", hidden, vocab);
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == BRAID_F32)
-        braid_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)table, ids, out, n_tokens, hidden, vocab);
+        braid_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)table, ids, out, n_tokens, hidden, vocab, scale);
     else if (table_dtype == BRAID_BF16)
-        braid_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab);
+        braid_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab, scale);
     else
         BRAID_REFUSE("embed: unknown table dtype code %d", table_dtype);
     BRAID_LAUNCH_CHECK();

@@ -1,0 +1,302 @@
+// Mixture of experts: routing, the plan that sorts a step's (token, choice) pairs by expert, the
+// experts' matrix products over those sorted rows, and the weighted sum back into the residual stream.
+//
+// Routing (one warp a token): s = softmax(z) over all experts; the experts form `groups` equal groups of
+// neighbours, a group's score is its largest s, and only experts of the `keep` best groups can be chosen;
+// the `top` allowed experts with the largest s are chosen (ties: the lower index); their weights are
+// their s divided by the sum of the chosen s (+ 1e-20), times `mult` (a constant factor the caller wants
+// on the layer's output).  Everything float32.
+//
+// The plan: every chosen (token, choice) pair gets a slot in an array ordered by expert, each expert's run
+// padded to a multiple of `tile` slots, so that a tile of slots belongs to one expert and the products can
+// run tile by tile with the sizes known only on the device.  Which slot of its expert's run a pair gets
+// does not touch any number: every output row is a sum over k in a fixed order whatever its slot.
+// Launch sizes depend on the step's shape alone (an upper bound of tiles), so a CUDA graph can replay them.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ routing
+struct MoeRouteArgs {
+    const float* logits;      // [rows, experts]
+    int* idx;                 // [rows, top]
+    float* wgt;               // [rows, top]
+    int rows, experts, top, groups, keep;
+    float mult;
+};
+
+#define MOE_ROUTE_WARPS 4
+
+__global__ void __launch_bounds__(MOE_ROUTE_WARPS * 32)
+moe_route_kernel(MoeRouteArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float smem[];          // per warp: [experts] scores, [groups] group scores
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * MOE_ROUTE_WARPS + warp;
+    if (row >= a.rows) return;
+    float* s = smem + (size_t)warp * (a.experts + a.groups);
+    float* gs = s + a.experts;
+    const float* z = a.logits + (size_t)row * a.experts;
+    float mx = -INFINITY;
+    for (int e = lane; e < a.experts; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < a.experts; e += 32) {
+        const float p = expf(z[e] - mx);
+        s[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < a.experts; e += 32) s[e] *= inv;
+    __syncwarp();
+    const int per = a.experts / a.groups;
+    for (int g = lane; g < a.groups; g += 32) {
+        float m = -INFINITY;
+        for (int i = 0; i < per; ++i) m = fmaxf(m, s[g * per + i]);
+        gs[g] = m;
+    }
+    __syncwarp();
+    // the `keep` best groups stay; the others are closed by marking their score negative
+    // (a kept group's score is made > 2, a softmax score never is)
+    for (int k = 0; k < a.keep; ++k) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int g = lane; g < a.groups; g += 32) {
+            const float v = gs[g];
+            if (v <= 2.f && (v > best || (v == best && g < bi))) { best = v; bi = g; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (lane == 0 && bi != 0x7fffffff) gs[bi] = 3.f;
+        __syncwarp();
+    }
+    // the `top` largest scores among experts of kept groups; a chosen expert's score is then hidden
+    float chosen_sum = 0.f;
+    for (int k = 0; k < a.top; ++k) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < a.experts; e += 32) {
+            const float v = s[e];
+            if (v >= 0.f && gs[e / per] > 2.f && (v > best || (v == best && e < bi))) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (bi == 0x7fffffff) { bi = -1; best = 0.f; }      // fewer allowed experts than `top`
+        if (lane == 0) {
+            a.idx[(size_t)row * a.top + k] = bi;
+            a.wgt[(size_t)row * a.top + k] = best;
+            if (bi >= 0) s[bi] = -1.f;
+        }
+        chosen_sum += best;
+        __syncwarp();
+    }
+    const float norm = a.mult / (chosen_sum + 1e-20f);
+    __syncwarp();
+    for (int k = lane; k < a.top; k += 32) a.wgt[(size_t)row * a.top + k] *= norm;
+}
+
+extern "C" int braid_moe_route(const float* logits, int* idx, float* wgt, int rows, int experts, int top,
+                               int groups, int keep, float mult, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (experts <= 0 || top <= 0 || top > experts) BRAID_REFUSE("moe_route: top=%d of %d experts", top, experts);
+    if (groups <= 0 || experts % groups || keep <= 0 || keep > groups) BRAID_REFUSE("moe_route: %d experts in %d groups, %d kept", experts, groups, keep);
+    const size_t smem = (size_t)MOE_ROUTE_WARPS * (experts + groups) * sizeof(float);
+    if (smem > 48 * 1024) BRAID_REFUSE("moe_route: %d experts are more than one block's shared memory holds", experts);
+    MoeRouteArgs a{logits, idx, wgt, rows, experts, top, groups, keep, mult};
+    braid_launch(moe_route_kernel, dim3((rows + MOE_ROUTE_WARPS - 1) / MOE_ROUTE_WARPS), dim3(MOE_ROUTE_WARPS * 32), smem,
+                 (cudaStream_t)stream, a);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ the plan
+// One block.  idx [rows * top] holds each pair's expert (-1: none); pairs of padding rows (token_seq < 0)
+// take no slot.  Outputs: slot_pair [cap] (pair of each slot, -1 for padding slots), pair_slot [rows * top]
+// (slot of each pair, -1 for none), tile_expert [max_tiles], meta[0] = tiles in use.
+#define MOE_MAX_EXPERTS 1024
+
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ idx, const int* __restrict__ token_seq, int* __restrict__ slot_pair,
+                int* __restrict__ pair_slot, int* __restrict__ tile_expert, int* __restrict__ meta,
+                int rows, int top, int experts, int tile, int max_tiles) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ int count[MOE_MAX_EXPERTS];
+    __shared__ int start[MOE_MAX_EXPERTS];
+    const int pairs = rows * top;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+    for (int i = threadIdx.x; i < max_tiles * tile; i += blockDim.x) slot_pair[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = (token_seq[i / top] >= 0) ? idx[i] : -1;
+        if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < experts; ++e) {
+            start[e] = run;
+            run += (count[e] + tile - 1) / tile;
+        }
+        meta[0] = run < max_tiles ? run : max_tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const int n = (count[e] + tile - 1) / tile;
+        for (int t = 0; t < n; ++t)
+            if (start[e] + t < max_tiles) tile_expert[start[e] + t] = e;
+        count[e] = 0;                       // from here on: the cursor within the expert's run
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = (token_seq[i / top] >= 0) ? idx[i] : -1;
+        int slot = -1;
+        if (e >= 0 && e < experts) {
+            slot = start[e] * tile + atomicAdd(&count[e], 1);
+            if (slot < max_tiles * tile) slot_pair[slot] = i; else slot = -1;
+        }
+        pair_slot[i] = slot;
+    }
+}
+
+extern "C" int braid_moe_plan(const int* idx, const int* token_seq, int* slot_pair, int* pair_slot, int* tile_expert,
+                              int* meta, int rows, int top, int experts, int tile, int max_tiles, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (experts <= 0 || experts > MOE_MAX_EXPERTS) BRAID_REFUSE("moe_plan: %d experts (at most %d)", experts, MOE_MAX_EXPERTS);
+    if (tile <= 0 || tile % 16) BRAID_REFUSE("moe_plan: the tile of %d slots must be a multiple of 16", tile);
+    braid_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, idx, token_seq, slot_pair, pair_slot,
+                 tile_expert, meta, rows, top, experts, tile, max_tiles);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ the experts' products, plain
+// Units of 16 slots x 64 outputs; 256 threads, each one slot and four outputs; float32 FMA in a fixed
+// order along k.  MODE 0: act[slot, j] = silu(x[token] . gate_e[j]) * (x[token] . up_e[j]), the input rows
+// gathered through slot_pair.  MODE 1: y[slot, j] = act[slot] . down_e[j].
+struct MoeGemmArgs {
+    const void* x;            // MODE 0: [rows, ldx] the layer's normed input; MODE 1: act [slots, ldx]
+    const void* w0;           // MODE 0: gate [experts, J, K]; MODE 1: down [experts, J, K]
+    const void* w1;           // MODE 0: up [experts, J, K]
+    void* out;                // [slots, ldo]
+    const int* slot_pair;
+    const int* tile_expert;
+    const int* meta;
+    long long ldx, ldo;
+    int J, K, top, tile;
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+moe_gemm_simt_kernel(MoeGemmArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float xs[16][16 + 1];        // [k][slot]
+    __shared__ float w0s[16][64 + 4];       // [k][output]
+    __shared__ float w1s[MODE == 0 ? 16 : 1][64 + 4];
+    const int unit = blockIdx.y;                             // 16 slots
+    const int t = unit * 16 / a.tile;
+    if (t >= a.meta[0]) return;
+    const int e = a.tile_expert[t];
+    const int slot0 = unit * 16;
+    const int m0 = blockIdx.x * 64;
+    const int ts = threadIdx.x >> 4, tj = threadIdx.x & 15;  // ts: slot, tj: group of four outputs
+    const int my_pair = a.slot_pair[slot0 + ts];
+    // the row this thread fetches for the x tile: thread (r = tid >> 4, c = tid & 15) loads x[slot r][k0 + c]
+    const long long src_row = (MODE == 0) ? (my_pair >= 0 ? my_pair / a.top : -1) : (slot0 + ts);
+    const T* w0 = (const T*)a.w0 + (size_t)e * a.J * a.K;
+    const T* w1 = (MODE == 0) ? (const T*)a.w1 + (size_t)e * a.J * a.K : nullptr;
+    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k0 = 0; k0 < a.K; k0 += 16) {
+        {
+            const int k = k0 + tj;
+            xs[tj][ts] = (src_row >= 0 && k < a.K) ? to_f32(((const T*)a.x)[(size_t)src_row * a.ldx + k]) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int el = threadIdx.x + i * 256;            // 0..1023: 64 outputs x 16 k
+            const int r = el >> 4, c = el & 15;
+            const int k = k0 + c, m = m0 + r;
+            const bool ok = (m < a.J && k < a.K);
+            w0s[c][r] = ok ? to_f32(w0[(size_t)m * a.K + k]) : 0.f;
+            if (MODE == 0) w1s[c][r] = ok ? to_f32(w1[(size_t)m * a.K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+            const float xv = xs[kk][ts];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc0[j] = fmaf(xv, w0s[kk][tj * 4 + j], acc0[j]);
+                if (MODE == 0) acc1[j] = fmaf(xv, w1s[kk][tj * 4 + j], acc1[j]);
+            }
+        }
+        __syncthreads();
+    }
+    T* o = (T*)a.out + (size_t)(slot0 + ts) * a.ldo;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int m = m0 + tj * 4 + j;
+        if (m >= a.J) continue;
+        if (MODE == 0) {
+            const float g = acc0[j];
+            o[m] = from_f32<T>(my_pair >= 0 ? g / (1.f + expf(-g)) * acc1[j] : 0.f);
+        } else {
+            o[m] = from_f32<T>(acc0[j]);
+        }
+    }
+}
+
+extern "C" int braid_moe_gemm_simt(const void* x, const void* w0, const void* w1, void* out, const int* slot_pair,
+                                   const int* tile_expert, const int* meta, int dtype, int mode, long long ldx,
+                                   long long ldo, int J, int K, int top, int tile, int max_tiles, void* stream) {
+    if (max_tiles <= 0 || J <= 0) return BRAID_OK;
+    if (K <= 0) BRAID_REFUSE("moe_gemm: k=%d must be positive", K);
+    if (tile <= 0 || tile % 16) BRAID_REFUSE("moe_gemm: the tile of %d slots must be a multiple of 16", tile);
+    MoeGemmArgs a{x, w0, w1, out, slot_pair, tile_expert, meta, ldx, ldo, J, K, top, tile};
+    const long long units = (long long)max_tiles * (tile / 16);
+    if (units > 65535) BRAID_REFUSE("moe_gemm: %lld units of 16 slots exceed the grid limit", units);
+    dim3 grid((J + 63) / 64, (unsigned)units);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32 && mode == 0) braid_launch(moe_gemm_simt_kernel<float, 0>, grid, dim3(256), 0, s, a);
+    else if (dtype == BRAID_F32 && mode == 1) braid_launch(moe_gemm_simt_kernel<float, 1>, grid, dim3(256), 0, s, a);
+    else if (dtype == BRAID_BF16 && mode == 0) braid_launch(moe_gemm_simt_kernel<__nv_bfloat16, 0>, grid, dim3(256), 0, s, a);
+    else if (dtype == BRAID_BF16 && mode == 1) braid_launch(moe_gemm_simt_kernel<__nv_bfloat16, 1>, grid, dim3(256), 0, s, a);
+    else BRAID_REFUSE("moe_gemm: unknown dtype %d or mode %d", dtype, mode);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ the weighted sum
+// h[row, :] += sum over the row's choices k, in the order of k, of wgt[row, k] * y[pair_slot[row, k], :].
+template <typename T>
+__global__ void moe_combine_kernel(float* __restrict__ h, const T* __restrict__ y, const int* __restrict__ pair_slot,
+                                   const float* __restrict__ wgt, int rows, int width, int top, long long ldy) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int slot = pair_slot[(size_t)row * top + k];
+            if (slot >= 0) acc = fmaf(wgt[(size_t)row * top + k], to_f32(y[(size_t)slot * ldy + c]), acc);
+        }
+        h[(size_t)row * width + c] += acc;
+    }
+}
+
+extern "C" int braid_moe_combine(float* h, const void* y, int y_dtype, const int* pair_slot, const float* wgt,
+                                 int rows, int width, int top, long long ldy, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (y_dtype == BRAID_F32) braid_launch(moe_combine_kernel<float>, dim3(rows), dim3(threads), 0, s, h, (const float*)y, pair_slot, wgt, rows, width, top, ldy);
+    else if (y_dtype == BRAID_BF16) braid_launch(moe_combine_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, s, h, (const __nv_bfloat16*)y, pair_slot, wgt, rows, width, top, ldy);
+    else BRAID_REFUSE("moe_combine: unknown dtype code %d", y_dtype);
+    BRAID_LAUNCH_CHECK();
+}

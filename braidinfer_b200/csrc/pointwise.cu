@@ -1,0 +1,93 @@
+// Element-wise kernels that models beside the dense Mistral decoder need: the Dynamic Tanh norm,
+// the soft cap of logits, and the side-by-side copy of two residual streams into one product's input.
+// All arithmetic is float32; inputs are the float32 residual stream or float32 logits.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ Dynamic Tanh
+// y[r, i] = tanh(alpha * (x[src(r), i] * in_scale)) * w[i] + b[i].  No mean and no variance: rows are
+// independent element by element.  alpha is one stored scalar.  `row_index` (may be null) picks the input
+// row of each output row; a negative index gives a row of zeros.  out may be x itself (TO = float).
+template <typename TW, typename TO>
+__global__ void dyt_kernel(const float* x, const TW* __restrict__ w, const TW* __restrict__ b,
+                           const TW* __restrict__ alpha, TO* out, const int* __restrict__ row_index,
+                           int rows, int width, float in_scale) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    if (r >= rows) return;
+    const int src = row_index ? row_index[r] : r;
+    TO* o = out + (size_t)r * width;
+    if (src < 0) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TO>(0.f);
+        return;
+    }
+    const float a = to_f32(alpha[0]) ;
+    const float* xr = x + (size_t)src * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        o[i] = from_f32<TO>(fmaf(tanhf(a * (xr[i] * in_scale)), to_f32(w[i]), to_f32(b[i])));
+}
+
+extern "C" int braid_dyt(const float* x, const void* w, const void* b, const void* alpha, int w_dtype,
+                         void* out, int out_dtype, const int* row_index, int rows, int width, float in_scale,
+                         void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (width <= 0) BRAID_REFUSE("dyt: width=%d must be positive", width);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 1024 ? 256 : 128;
+#define BRAID_DYT(TW, TO) braid_launch(dyt_kernel<TW, TO>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (const TW*)b, (const TW*)alpha, (TO*)out, row_index, rows, width, in_scale)
+    if (w_dtype == BRAID_F32 && out_dtype == BRAID_F32) BRAID_DYT(float, float);
+    else if (w_dtype == BRAID_F32 && out_dtype == BRAID_BF16) BRAID_DYT(float, __nv_bfloat16);
+    else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_F32) BRAID_DYT(__nv_bfloat16, float);
+    else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_BF16) BRAID_DYT(__nv_bfloat16, __nv_bfloat16);
+    else BRAID_REFUSE("dyt: unknown dtype codes w=%d out=%d", w_dtype, out_dtype);
+#undef BRAID_DYT
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ soft cap
+// x <- cap * tanh(x / cap), in place, float32.
+__global__ void softcap_kernel(float* x, long long total, float cap, float inv_cap) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+extern "C" int braid_softcap(float* x, long long total, float cap, void* stream) {
+    if (total <= 0) return BRAID_OK;
+    if (!(cap > 0.f)) BRAID_REFUSE("softcap: the cap must be positive, got %g", (double)cap);
+    const int threads = 256;
+    const long long blocks = (total + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("softcap: %lld elements exceed one launch", total);
+    braid_launch(softcap_kernel, dim3((int)blocks), dim3(threads), 0, (cudaStream_t)stream, x, total, cap, 1.f / cap);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ two streams side by side
+// out[r, 0:w] = a[r, :], out[r, w:2w] = b[r, :], float32 in, TO out.
+template <typename TO>
+__global__ void concat2_kernel(const float* __restrict__ a, const float* __restrict__ b, TO* __restrict__ out,
+                               long long total, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long r = i / (2 * width);
+    const int c = (int)(i - r * 2 * width);
+    out[i] = from_f32<TO>(c < width ? a[r * width + c] : b[r * width + c - width]);
+}
+
+extern "C" int braid_concat2(const float* a, const float* b, void* out, int out_dtype, int rows, int width,
+                             void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (width <= 0) BRAID_REFUSE("concat2: width=%d must be positive", width);
+    const long long total = (long long)rows * 2 * width;
+    const int threads = 256;
+    const long long blocks = (total + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("concat2: %lld elements exceed one launch", total);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == BRAID_F32) braid_launch(concat2_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, a, b, (float*)out, total, width);
+    else if (out_dtype == BRAID_BF16) braid_launch(concat2_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, a, b, (__nv_bfloat16*)out, total, width);
+    else BRAID_REFUSE("concat2: unknown dtype code %d", out_dtype);
+    BRAID_LAUNCH_CHECK();
+}

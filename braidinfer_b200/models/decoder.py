@@ -9,7 +9,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts.base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS
+from ..parts.base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, MIXERS, NORMS
 from ..parts.spec import CacheRequest, ModelSpec, TensorSpec
 
 
@@ -28,12 +28,19 @@ class DecoderModel:
                 ffn = FEED_FORWARDS.get(ls.feed_forward.kind)(ls.feed_forward.params, ls.prefix, runtime)
                 ffn_norm = NORMS.get(ls.feed_forward_norm.kind)(ls.feed_forward_norm.params, ls.prefix, runtime)
             self.blocks.append(BLOCKS.get(ls.block)(mixer, mixer_norm, ffn, ffn_norm))
+        self.injection = None
+        if spec.injection is not None:
+            self.injection = INJECTIONS.get(spec.injection.kind)(spec.injection.params, "", runtime)
+        # the embedding's output must outlive the layers, which add into the stream in place
+        self._keep_h0 = any(e.inject for e in spec.schedule)
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, "", runtime)
         self.head = HEADS.get(spec.head.kind)(spec.head.params, "", runtime)
 
     # ------------------------------------------------------------------ weights
     def all_parts(self):
         yield self.embedding
+        if self.injection is not None:
+            yield self.injection
         for b in self.blocks:
             yield from b.parts()
         yield self.final_norm
@@ -74,7 +81,10 @@ class DecoderModel:
         h = self.embedding.forward(ctx.token_ids, ctx.rows)
         if tap is not None:
             tap(0, h)
+        h0 = h.clone() if self._keep_h0 else None
         for e, entry in enumerate(self.spec.schedule):
+            if entry.inject:
+                h = self.injection.forward(ctx.resolve(h), h0, ctx)
             view = cache.layer_view(e)
             if view is not None:
                 view.page_table = ctx.page_tables[view.group]

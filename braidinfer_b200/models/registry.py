@@ -29,11 +29,13 @@ def register_architecture(arch: Architecture) -> Architecture:
 
 
 def architecture_for(config_dict: Mapping[str, Any]) -> Architecture:
-    """Look the model up by config.json["architectures"][0]."""
+    """Look the model up by config.json["architectures"][0], or by config.json["architecture"] (one name)."""
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]
     if not archs or not isinstance(archs, (list, tuple)) or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names; "
-                          f"known architectures: {sorted(ARCHITECTURES)}")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one "
+                          f"name); known architectures: {sorted(ARCHITECTURES)}")
     name = archs[0]
     if name not in ARCHITECTURES:
         raise UnknownArchitectureError(

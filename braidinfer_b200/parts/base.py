@@ -122,6 +122,16 @@ class Head(Part):
         raise NotImplementedError
 
 
+class Injection(Part):
+    """Mixes the embedding's output back into the stream before the runs that ask for it
+    (`ScheduleEntry.inject`)."""
+
+    def forward(self, h: torch.Tensor, h0: torch.Tensor, ctx) -> torch.Tensor:
+        """h: the stream [rows, width] float32 (complete: no sum is deferred on it); h0: the embedding's
+        output, float32, which must not be written.  Returns the new stream, float32 (a new tensor or h)."""
+        raise NotImplementedError
+
+
 class Block:
     """The arrangement of a layer's parts.  `forward(h, ctx, cache, state) -> h` runs them on
     the float32 residual stream; `cache` and `state` are the mixer's (see Mixer.forward).
@@ -175,3 +185,4 @@ POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
+INJECTIONS = Registry("injection")

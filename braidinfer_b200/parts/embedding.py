@@ -1,7 +1,9 @@
 """Token embedding and output head.
 
 Embedding: h[t, :] = float(E[token_t, :]), no scale (reference:
-kernels/megakernel_ops.hip:1757-1768).  Head: logits = W h in float32
+kernels/megakernel_ops.hip:1757-1768); a model may name a constant factor on the rows (`scale`) and a
+norm of the scaled rows (`norm`), whose output is then the stream.  A model may also cap its logits:
+logits <- cap * tanh(logits / cap) (`softcap`).  Head: logits = W h in float32
 (kernels/megakernel_ops.hip:1783-1835); W is lm_head.weight, or the embedding table
 when the model ties them (crates/braidinfer-runtime/src/model/model_load.rs:388-398).
 """
@@ -11,37 +13,49 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import EMBEDDINGS, HEADS, Embedding, Head
+from .base import EMBEDDINGS, HEADS, NORMS, Embedding, Head
 from .linear import Linear
 from .spec import TensorSpec
 
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    """params: vocab_size, hidden_size, name."""
+    """params: vocab_size, hidden_size, name; optional scale (a factor on the rows, default 1) and norm
+    (a PartSpec of a norm whose `forward` takes `in_place=True`, applied to the scaled rows)."""
 
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
         self.name = prefix + params.get("name", "model.embed_tokens.weight")
+        self.scale = float(params.get("scale", 1.0))
+        norm = params.get("norm")
+        self.norm = NORMS.get(norm.kind)(norm.params, prefix, runtime) if norm is not None else None
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {self.name: TensorSpec((self.vocab, self.hidden))}
+        d = {self.name: TensorSpec((self.vocab, self.hidden))}
+        if self.norm is not None:
+            d.update(self.norm.tensor_specs())
+        return d
 
     def load(self, tensors) -> None:
         self.weight = tensors[self.name]
+        if self.norm is not None:
+            self.norm.load(tensors)
 
     def forward(self, token_ids: torch.Tensor, rows: int) -> torch.Tensor:
         h = torch.empty((rows, self.hidden), dtype=torch.float32, device=self.rt.device)
-        self.rt.kernels.embed(self.weight, token_ids, h)
+        self.rt.kernels.embed(self.weight, token_ids, h, scale=self.scale)
+        if self.norm is not None:
+            h = self.norm.forward(h, None, in_place=True)
         return h
 
 
 @HEADS.register("linear_head")
 class LinearHead(Head):
-    """params: vocab_size, hidden_size, name, tied (use the embedding table)."""
+    """params: vocab_size, hidden_size, name, tied (use the embedding table, as stored: a factor that the
+    embedding puts on its rows is not part of the table), softcap (a positive cap on the logits, or None)."""
 
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
@@ -51,6 +65,8 @@ class LinearHead(Head):
         self.tied = params.get("tied", False)
         self.name = prefix + params.get("name", "lm_head.weight")
         self.linear = Linear(runtime, [self.name], [self.vocab], self.hidden)
+        cap = params.get("softcap")
+        self.softcap = float(cap) if cap else None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         if self.tied:
@@ -70,4 +86,7 @@ class LinearHead(Head):
         self.linear.share(embedding_weight)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.linear.forward(x, out_dtype=torch.float32)
+        logits = self.linear.forward(x, out_dtype=torch.float32)
+        if self.softcap is not None:
+            self.rt.kernels.softcap(logits, self.softcap)
+        return logits

@@ -1,0 +1,123 @@
+"""Latent attention: one low-rank vector per token stands for the keys and values of all heads.
+
+For the mixer's input x (a row per token):
+    q            = Wq x                      per head [dim unrotated | rot_dim rotated] numbers
+    [c' ; kr']   = Wdkv x                    kv_rank + rot_dim numbers
+    c            = c' / sqrt(mean(c'^2) + eps) * w_norm           (the latent)
+    kr           = rotate(kr', position)     (one rotated key part, shared by all heads)
+    head h:  key = [Wuk_h c ; kr],  value = Wuv_h c
+    score(i, j)  = (q_u(i) . Wuk_h c(j) + rotate(q_r(i)) . kr(j)) * scale,   j <= i, softmax over j
+    out          = Wo concat_h( sigmoid(Wg x)_h * sum_j p(i, j) Wuv_h c(j) )
+(Multi-head latent attention as in DeepSeek-AI, "DeepSeek-V2", 2024; the output gate per head is this
+part's own option.)  Only c and kr are cached: kv_rank + rot_dim numbers a token, whatever the head count.
+
+The cache is never expanded into keys and values.  q_u . (Wuk_h c) = (Wuk_h^T q_u) . c, so each query
+head is carried into the latent space (`gemm_heads` with Wuk_h^T), attention runs as multi-query
+attention over the cached rows (key: the whole row; value: its first kv_rank numbers), and the head's
+output is Wuv_h applied to the attended latent (`gemm_heads` again, with the gate in its epilogue).  Wuk
+and Wuv are used as stored; per-head transposes are made once at load, no product of weights is formed.
+
+A constant factor on the mixer's output (`out_mult`, a model's residual multiplier) rides on the gate.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .base import MIXERS, POSITION_ENCODINGS, Mixer
+from .linear import Linear
+from .spec import CacheRequest, PartSpec, TensorSpec
+
+
+@MIXERS.register("latent_attention")
+class LatentAttention(Mixer):
+    """params: hidden_size, num_heads, dim (unrotated query/key numbers a head), rot_dim (rotated ones),
+    vdim (value size a head), kv_rank, scale (on the scores), eps (of the latent's RMS norm), window
+    (int | None), out_mult (default 1), gated (default True), position_encoding (a PartSpec of kind "rope"
+    with head_dim = rot_dim: its rope_dim leading numbers of the rotated part turn), and the tensor names
+    q, dkv, dkv_norm, uk, uv, g, o (under the prefix)."""
+
+    def __init__(self, params, prefix, runtime) -> None:
+        super().__init__(params, prefix, runtime)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.heads = int(p["num_heads"])
+        self.dim = int(p["dim"])
+        self.rot = int(p["rot_dim"])
+        self.vdim = int(p["vdim"])
+        self.rank = int(p["kv_rank"])
+        self.scale = float(p["scale"])
+        self.eps = float(p["eps"])
+        self.window = p.get("window")
+        self.out_mult = float(p.get("out_mult", 1.0))
+        self.gated = bool(p.get("gated", True))
+        pe: PartSpec = p["position_encoding"]
+        self.pe = POSITION_ENCODINGS.get(pe.kind)(pe.params, prefix, runtime)
+        if self.pe.head_dim != self.rot or getattr(self.pe, "pairing", "half") != "half":
+            raise ValueError("latent_attention rotates the rot_dim part of queries and the shared key part, "
+                             "element i with element i + rope_dim / 2")
+        self.q_cols = self.heads * (self.dim + self.rot)
+        self.D = self.rank + self.rot
+        names = [prefix + p.get("q", "mix.q"), prefix + p.get("dkv", "mix.dkv")]
+        outs = [self.q_cols, self.D]
+        if self.gated:
+            names.append(prefix + p.get("g", "mix.g"))
+            outs.append(self.heads)
+        self.proj = Linear(runtime, names, outs, self.hidden)          # one stacked product: q, [c' ; kr'], gate
+        self.norm_name = prefix + p.get("dkv_norm", "mix.dkv.norm")
+        self.uk_name = prefix + p.get("uk", "mix.uk")
+        self.uv_name = prefix + p.get("uv", "mix.uv")
+        self.o = Linear(runtime, [prefix + p.get("o", "mix.o")], [self.hidden], self.heads * self.vdim)
+        self.norm_w = self.uk_t = self.uv = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        d = dict(self.proj.tensor_specs())
+        d[self.norm_name] = TensorSpec((self.rank,), init="one_plus_normal")
+        d[self.uk_name] = TensorSpec((self.heads * self.dim, self.rank))
+        d[self.uv_name] = TensorSpec((self.heads * self.vdim, self.rank))
+        d.update(self.o.tensor_specs())
+        d.update(self.pe.tensor_specs())
+        return d
+
+    def load(self, tensors) -> None:
+        self.proj.load(tensors)
+        w = self.proj.weight
+        pad = -w.shape[0] % 8            # rows of zeros, so that a row of the stacked result starts on 16 bytes
+        if pad:
+            self.proj.weight = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)]).contiguous()
+        self.o.load(tensors)
+        self.pe.load(tensors)
+        self.norm_w = tensors[self.norm_name]
+        # [heads, kv_rank, dim]: head h's matrix that carries q_u into the latent space, [out, in]
+        self.uk_t = tensors[self.uk_name].view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.uv = tensors[self.uv_name].view(self.heads, self.vdim, self.rank).contiguous()
+
+    def cache_request(self) -> Optional[CacheRequest]:
+        return CacheRequest("window" if self.window else "full", 1, self.D, self.window, planes=1)
+
+    def forward(self, x, residual, ctx, cache, state):
+        if cache is None:
+            raise RuntimeError("latent_attention needs a cache view")
+        K = self.rt.kernels
+        rows = x.shape[0]
+        proj = self.proj.forward(x)                                   # [rows, q | c' kr' | gate | padding]
+        q_lat = self.rt.empty(rows, self.heads, self.D)
+        writable = not cache.read_only
+        K.latent_prep(proj, self.q_cols, self.norm_w, self.pe.inv_freq, ctx.positions, ctx.token_seq,
+                      cache.page_table if writable else None, cache.storage if writable else None, q_lat,
+                      self.heads, self.dim, self.rot, self.rank, self.pe.rope_dim, cache.page_size, self.eps)
+        q_u = proj[:, :self.q_cols].view(rows, self.heads, self.dim + self.rot)[:, :, :self.dim]
+        K.gemm_heads(q_u, self.uk_t, q_lat[:, :, :self.rank])
+        o_lat = self.rt.empty(rows, self.heads, self.rank)
+        self._attend(q_lat, o_lat, ctx, cache)
+        out = self.rt.empty(rows, self.heads * self.vdim)
+        gate = proj[:, self.q_cols + self.D:self.q_cols + self.D + self.heads] if self.gated else None
+        if gate is None and self.out_mult != 1.0:
+            raise RuntimeError("latent_attention: an output factor needs the gate's epilogue")
+        K.gemm_heads(o_lat, self.uv, out.view(rows, self.heads, self.vdim), gate=gate, mult=self.out_mult)
+        return self.o.forward(out, residual=residual, defer_to=ctx)
+
+    def _attend(self, q_lat, o_lat, ctx, cache) -> None:
+        self.rt.kernels.attn_latent_simple(q_lat, o_lat, cache.storage, cache.page_table, ctx.positions, ctx.token_seq,
+                                           self.rank, self.window, self.scale)

@@ -1,0 +1,94 @@
+"""Mixture of experts: each token is sent to a few small SwiGLU feed-forwards and gets back the
+weighted sum of their outputs.
+
+    z = Wr x (float32)          s = softmax(z) over all experts
+    experts form `groups` equal groups of neighbours; a group's score is its largest s; only experts of
+    the `keep` best groups can be chosen; the `top` allowed experts with the largest s are chosen
+    weight_k = s_k / (sum of the chosen s + 1e-20)
+    out = sum_k weight_k * Wdown_k ( silu(Wgate_k x) * (Wup_k x) )
+(Group-limited routing as in DeepSeek-AI, "DeepSeek-V2", 2024.)  Router scores, the choice, the weights
+and the weighted sum are float32.
+
+A step's (token, choice) pairs are sorted by expert on the device (`moe_plan`), the experts' products run
+over the sorted rows tile by tile, and the weighted sum adds a token's choices in their fixed order, so
+what a token gets does not depend on its neighbours in the batch.  Nothing is read back by the host, and
+launch sizes follow from the step's shape alone.  A constant factor on the output (`out_mult`) rides on
+the weights.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .base import FEED_FORWARDS, FeedForward
+from .linear import Linear
+from .spec import TensorSpec
+
+
+@FEED_FORWARDS.register("moe")
+class MixtureOfExperts(FeedForward):
+    """params: hidden_size, intermediate_size (of one expert), experts, top, groups (default 1), keep
+    (groups kept, default all), out_mult (default 1), and tensor names: router, and expert_gate, expert_up,
+    expert_down as patterns with `{e}` for the expert's number."""
+
+    def __init__(self, params, prefix, runtime) -> None:
+        super().__init__(params, prefix, runtime)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        self.experts = int(p["experts"])
+        self.top = int(p["top"])
+        self.groups = int(p.get("groups", 1))
+        self.keep = int(p.get("keep", self.groups))
+        self.out_mult = float(p.get("out_mult", 1.0))
+        if self.experts % self.groups:
+            raise ValueError(f"{self.experts} experts do not form {self.groups} equal groups")
+        if not (1 <= self.keep <= self.groups):
+            raise ValueError(f"{self.keep} groups kept of {self.groups}")
+        if not (1 <= self.top <= self.keep * (self.experts // self.groups)):
+            raise ValueError(f"top {self.top} of {self.keep} groups of {self.experts // self.groups} experts")
+        self.router = Linear(runtime, [prefix + p.get("router", "mlp.router")], [self.experts], self.hidden)
+        self.gate_names = [prefix + p.get("expert_gate", "mlp.e{e}.gate").format(e=e) for e in range(self.experts)]
+        self.up_names = [prefix + p.get("expert_up", "mlp.e{e}.up").format(e=e) for e in range(self.experts)]
+        self.down_names = [prefix + p.get("expert_down", "mlp.e{e}.down").format(e=e) for e in range(self.experts)]
+        self.w_gate = self.w_up = self.w_down = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        d = dict(self.router.tensor_specs())
+        for e in range(self.experts):
+            d[self.gate_names[e]] = TensorSpec((self.inter, self.hidden))
+            d[self.up_names[e]] = TensorSpec((self.inter, self.hidden))
+            d[self.down_names[e]] = TensorSpec((self.hidden, self.inter))
+        return d
+
+    def load(self, tensors) -> None:
+        self.router.load(tensors)
+        self.w_gate = torch.stack([tensors[n] for n in self.gate_names]).contiguous()     # [experts, inter, hidden]
+        self.w_up = torch.stack([tensors[n] for n in self.up_names]).contiguous()
+        self.w_down = torch.stack([tensors[n] for n in self.down_names]).contiguous()     # [experts, hidden, inter]
+
+    def tile(self, rows: int) -> int:
+        """Slots a tile of the plan: 16 while an expert sees few rows, 64 beyond."""
+        return 16 if rows * self.top <= 16 * self.experts else 64
+
+    def forward(self, x, residual, ctx):
+        K = self.rt.kernels
+        rows = x.shape[0]
+        logits = self.router.forward(x, out_dtype=torch.float32)
+        idx = torch.empty((rows, self.top), dtype=torch.int32, device=x.device)
+        wgt = torch.empty((rows, self.top), dtype=torch.float32, device=x.device)
+        K.moe_route(logits, idx, wgt, self.groups, self.keep, mult=self.out_mult)
+        tile = self.tile(rows)
+        plan = K.moe_plan(idx, ctx.token_seq, self.experts, tile)
+        slots = plan[4] * tile
+        act = self.rt.empty(slots, self.inter)
+        y = self.rt.empty(slots, self.hidden)
+        self._experts(x, act, y, plan, tile)
+        K.moe_combine(residual, y, plan, wgt)
+        return residual
+
+    def _experts(self, x, act, y, plan, tile) -> None:
+        K = self.rt.kernels
+        K.moe_gemm_simt(x, self.w_gate, self.w_up, act, plan, self.top, tile)
+        K.moe_gemm_simt(act, self.w_down, None, y, plan, self.top, tile)

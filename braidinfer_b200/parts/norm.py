@@ -1,4 +1,10 @@
-"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, plain w
+"""Norms of the residual stream.
+
+Dynamic Tanh ("dyt"): y = tanh(alpha * x) * w + b, element by element, with one stored scalar alpha, a
+weight and a bias vector: no mean, no variance, nothing shared along a row (Zhu, Chen, He, LeCun, Liu:
+"Transformers without Normalization", 2025).  tanh and the products are float32.
+
+RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, plain w
 (reference: kernels/megakernel_ops.hip:862-904; `1 + w` is another model family's rule,
 crates/braidinfer-runtime/src/config.rs:552).  Reads the float32 residual stream, writes
 the run's element type; the sum of squares and the scale are float32."""
@@ -53,4 +59,36 @@ class RMSNorm(Norm):
             self.rt.kernels.streamk_reduce_norm(handle, x, self.weight, out, self.eps, row_index=row_index)
         else:
             self.rt.kernels.rmsnorm(x, self.weight, out, self.eps, row_index=row_index)
+        return out
+
+
+@NORMS.register("dyt")
+class DynamicTanh(Norm):
+    """params: width, name (the weight's tensor name under the prefix; the bias is name + ".b", the scalar
+    name + ".alpha")."""
+
+    def __init__(self, params, prefix, runtime) -> None:
+        super().__init__(params, prefix, runtime)
+        self.width = int(params["width"])
+        self.name = prefix + params["name"]
+        self.weight = self.bias = self.alpha = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.width,), init="one_plus_normal"),
+                self.name + ".b": TensorSpec((self.width,)),
+                self.name + ".alpha": TensorSpec((), init="one_plus_normal")}
+
+    def load(self, tensors) -> None:
+        self.weight, self.bias, self.alpha = tensors[self.name], tensors[self.name + ".b"], tensors[self.name + ".alpha"]
+
+    def forward(self, x: torch.Tensor, ctx=None, row_index: Optional[torch.Tensor] = None,
+                rows: Optional[int] = None, in_place: bool = False, in_scale: float = 1.0) -> torch.Tensor:
+        """`in_place`: x itself is overwritten and stays float32 (an embedding's norm: its output is the
+        stream).  `in_scale`: a constant factor on x that the caller has not applied yet."""
+        if in_place:
+            self.rt.kernels.dyt(x, self.weight, self.bias, self.alpha, x, in_scale=in_scale)
+            return x
+        n = rows if rows is not None else x.shape[0]
+        out = self.rt.empty(n, self.width)
+        self.rt.kernels.dyt(x, self.weight, self.bias, self.alpha, out, row_index=row_index, in_scale=in_scale)
         return out

@@ -32,9 +32,11 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  `cache_of` names an earlier schedule entry whose
-    cache this run reads instead of keeping its own."""
+    cache this run reads instead of keeping its own.  `inject`: the model's injection
+    (`ModelSpec.injection`) is applied to the stream right before this run."""
     layer: int
     cache_of: Optional[int] = None
+    inject: bool = False
 
 
 @dataclass(frozen=True)
@@ -50,8 +52,14 @@ class ModelSpec:
     max_position: int = 0                      # longest sequence the model is meant for (0: not stated)
     eos_token_ids: Tuple[int, ...] = ()        # tokens that end a sequence unless the caller names others
     bos_token_id: Optional[int] = None         # put before a text prompt by the command line
+    # A part (registry INJECTIONS) that mixes the embedding's output back into the stream before the runs
+    # that ask for it (`ScheduleEntry.inject`): a block of layers that runs several times in a row, for one,
+    # is fed the stream and the embedding's output anew at the start of every pass.
+    injection: Optional[PartSpec] = None
 
     def validate(self) -> None:
+        if self.injection is None and any(e.inject for e in self.schedule):
+            raise ValueError("a schedule entry asks for the injection, and the model has none")
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.layers)):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, which does not exist")
@@ -71,7 +79,7 @@ class TensorSpec:
     """A tensor that a part needs from the model folder.
 
     `init` tells the random-weights mode how to draw it: "normal" is N(0, std),
-    "one_plus_normal" is 1 + N(0, std).  `integer` marks index tables, which are
+    "one_plus_normal" is 1 + N(0, std).  A shape of () is one stored scalar.  `integer` marks index tables, which are
     kept as int32 whatever the run's dtype.
     """
     shape: Tuple[int, ...]
@@ -87,12 +95,14 @@ class CacheRequest:
 
     kind "full": keys and values of every past token; "window": of the last
     `window` tokens only.  Layers whose requests are equal share one group of
-    storage.
+    storage.  `planes` is how many vectors of `head_dim` a token and kv head keep:
+    2 for a key and a value, 1 where one vector serves as both (a latent).
     """
     kind: str
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
     def group_key(self) -> Tuple:
-        return (self.kind, self.num_kv_heads, self.head_dim, self.window)
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.planes)
