@@ -402,6 +402,8 @@ class Kernels:
                 lib.braid_latent_prep.argtypes = [c_void_p, c_longlong, c_int] + [c_void_p] * 7 + [c_int] * 10 + \
                                                  [c_float, c_void_p, c_void_p]
                 lib.braid_gemm_heads.argtypes = [c_void_p] * 4 + [c_int] * 5 + [c_longlong] * 5 + [c_float, c_void_p]
+                lib.braid_gemm_heads_mma.argtypes = [c_void_p] * 4 + [c_int] * 4 + [c_longlong] * 5 + [c_float, c_void_p]
+                lib.braid_gemm_heads_mma.restype = c_int
                 lib.braid_attn_latent_simple.argtypes = [c_void_p, c_void_p, c_int] + [c_void_p] * 4 + \
                                                         [c_longlong, c_longlong] + [c_int] * 8 + [c_float, c_void_p, c_void_p]
                 names = ("braid_latent_prep", "braid_gemm_heads", "braid_attn_latent_simple")
@@ -412,6 +414,8 @@ class Kernels:
                                                    [c_void_p]
                 lib.braid_moe_combine.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                                   c_longlong, c_void_p]
+                lib.braid_moe_gemm_mma.argtypes = [c_void_p] * 7 + [c_int, c_longlong, c_longlong] + [c_int] * 5 + [c_void_p]
+                lib.braid_moe_gemm_mma.restype = c_int
                 names = ("braid_moe_route", "braid_moe_plan", "braid_moe_gemm_simt", "braid_moe_combine")
             else:
                 names = ()
@@ -450,10 +454,11 @@ class Kernels:
             float(eps), self._error_flag.data_ptr(), self._stream()), "latent_prep")
 
     def gemm_heads(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
-                   mult: float = 1.0) -> None:
+                   mult: float = 1.0, tensor_cores: bool = True) -> None:
         """out[n, h, :] = w[h] x[n, h, :] for every head: x [rows, heads, K] and out [rows, heads, J] may be views
         (last dimension contiguous), w [heads, J, K] contiguous.  `gate` [rows, heads] (a view is fine): the result is
-        multiplied by mult * sigmoid(gate)."""
+        multiplied by mult * sigmoid(gate).  bfloat16 operands whose rows start on 16 bytes run on the tensor cores
+        unless `tensor_cores` is false; everything else on the plain kernel."""
         lib = self.part_library("latent")
         rows, heads, k = x.shape
         if w.dim() != 3 or w.shape[0] != heads or w.shape[2] != k or not w.is_contiguous():
@@ -466,6 +471,13 @@ class Kernels:
         if gate is not None and (tuple(gate.shape) != (rows, heads) or gate.stride(1) != 1):
             raise KernelError("gemm_heads: gate must be [rows, heads] with contiguous heads")
         self.launches += 1
+        if (tensor_cores and x.dtype == torch.bfloat16 and k % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 4 == 0):
+            self._check_lib(lib, lib.braid_gemm_heads_mma(
+                x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(gate), rows, heads, j, k, x.stride(0), x.stride(1),
+                out.stride(0), out.stride(1), gate.stride(0) if gate is not None else 0, float(mult), self._stream()),
+                "gemm_heads_mma")
+            return
         self._check_lib(lib, lib.braid_gemm_heads(
             x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(gate), dtype_code(x.dtype), rows, heads, j, k,
             x.stride(0), x.stride(1), out.stride(0), out.stride(1), gate.stride(0) if gate is not None else 0,
@@ -547,6 +559,83 @@ class Kernels:
             x.data_ptr(), w0.data_ptr(), _ptr(w1), out.data_ptr(), slot_pair.data_ptr(), tile_expert.data_ptr(),
             meta.data_ptr(), dtype_code(x.dtype), 0 if w1 is not None else 1, x.stride(0), out.stride(0), j, k, top, tile,
             max_tiles, self._stream()), "moe_gemm_simt")
+
+    @staticmethod
+    def moe_gemm_mma_eligible(x: torch.Tensor, w0: torch.Tensor, tile: int) -> bool:
+        return (x.dtype == torch.bfloat16 and w0.dtype == torch.bfloat16 and w0.shape[2] % 8 == 0 and x.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0 and w0.data_ptr() % 16 == 0 and tile in (16, 64))
+
+    def moe_gemm_mma(self, x: torch.Tensor, w0: torch.Tensor, w1: Optional[torch.Tensor], out: torch.Tensor, plan,
+                     top: int, tile: int) -> None:
+        """`moe_gemm_simt` in bfloat16 on the tensor cores; the plan's tile (16 or 64 slots) is the CTA's."""
+        lib = self.part_library("moe")
+        slot_pair, _pair_slot, tile_expert, meta, max_tiles = plan
+        j, k = w0.shape[1], w0.shape[2]
+        if not self.moe_gemm_mma_eligible(x, w0, tile) or not w0.is_contiguous() or (w1 is not None and (
+                not w1.is_contiguous() or w1.shape != w0.shape or w1.dtype != w0.dtype or w1.data_ptr() % 16)):
+            raise KernelError("moe_gemm_mma: bfloat16 operands, k and row strides in multiples of 8, starts on 16 bytes")
+        if x.shape[1] != k or out.shape[1] != j or out.shape[0] != max_tiles * tile or out.dtype != torch.bfloat16 \
+                or x.stride(1) != 1 or out.stride(1) != 1 or out.data_ptr() % 4:
+            raise KernelError("moe_gemm_mma: shapes do not fit")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_moe_gemm_mma(
+            x.data_ptr(), w0.data_ptr(), _ptr(w1), out.data_ptr(), slot_pair.data_ptr(), tile_expert.data_ptr(),
+            meta.data_ptr(), 0 if w1 is not None else 1, x.stride(0), out.stride(0), j, k, top, tile, max_tiles,
+            self._stream()), "moe_gemm_mma")
+
+    @staticmethod
+    def attn_latent_mma_supports(rank: int, rot: int) -> bool:
+        """Latent sizes the tensor-core attention is compiled for: kv_rank and rot_dim in multiples of 16, a rank
+        above 256 in multiples of 256, and a query tile plus two key tiles within one SM's shared memory."""
+        return (rank % 16 == 0 and rot % 16 == 0 and rank > 0 and (rank <= 256 or rank % 256 == 0)
+                and 128 * (rank + rot + 8) * 2 <= 227 * 1024)
+
+    def latent_attention_library(self, rank: int, rot: int):
+        key = ("latattn", rank, rot)
+        lib = self._part_libs.get(key)
+        if lib is None:
+            if not self.attn_latent_mma_supports(rank, rot):
+                raise KernelError(f"the tensor-core latent attention is not built for kv_rank {rank}, rot_dim {rot}")
+            lib = ctypes.CDLL(str(build.latent_attention_library(rank, rot, verbose=self._verbose)))
+            lib.braid_last_error.restype = c_char_p
+            lib.braid_latent_attn_mma.restype = c_int
+            lib.braid_latent_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 8 + [c_float, c_void_p, c_void_p]
+            lib.braid_latent_attn_partial_floats.restype = c_longlong
+            lib.braid_latent_attn_partial_floats.argtypes = [c_int, c_int, c_int]
+            lib.vparts = lib.braid_latent_attn_vparts()
+            if (lib.braid_latent_attn_rank(), lib.braid_latent_attn_rot()) != (rank, rot):
+                raise KernelError("the latent attention library was built for another size")
+            self._part_libs[key] = lib
+        return lib
+
+    def attn_latent_mma(self, q_lat: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
+                        q_start: torch.Tensor, q_len: torch.Tensor, kv_before: torch.Tensor, token_seq: torch.Tensor,
+                        n_seqs: int, max_q_len: int, rank: int, window: Optional[int], scale: float,
+                        n_splits: int = 1) -> None:
+        """`attn_latent_simple` in bfloat16 on the tensor cores.  Rows of padding are not written.  `n_splits` > 1
+        slices the context (steps of few tokens) and merges the slices in a second kernel."""
+        rows, heads, d = q_lat.shape
+        lib = self.latent_attention_library(rank, d - rank)
+        self._check_pages(cache)
+        if q_lat.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
+                or not q_lat.is_contiguous() or not out.is_contiguous() or tuple(out.shape) != (rows, heads, rank) \
+                or cache.dim() != 5 or cache.shape[1] != 1 or cache.shape[2] != 1 or cache.shape[4] != d:
+            raise KernelError("attn_latent_mma: contiguous bfloat16 q_lat [rows, heads, D], out [rows, heads, rank] and "
+                              "a cache [pages, 1, 1, page_size, D]")
+        partial = None
+        if n_splits > 1:
+            need = lib.braid_latent_attn_partial_floats(rows, heads, n_splits)
+            if self._attn_partial is None or self._attn_partial.numel() < need:
+                self._attn_partial = torch.empty(max(need, 1 << 22), dtype=torch.float32, device="cuda")
+                self.workspace_generation += 1
+            partial = self._attn_partial
+            self.launches += 1
+        self.launches += 1
+        self._check_lib(lib, lib.braid_latent_attn_mma(
+            q_lat.data_ptr(), out.data_ptr(), _ptr(partial), cache.data_ptr(), page_table.data_ptr(), q_start.data_ptr(),
+            q_len.data_ptr(), kv_before.data_ptr(), token_seq.data_ptr(), rows, n_seqs, max_q_len, heads,
+            page_table.shape[1], cache.shape[0], int(window or 0), n_splits, float(scale),
+            self._error_flag.data_ptr() + 16, self._stream()), "attn_latent_mma")
 
     def moe_combine(self, h: torch.Tensor, y: torch.Tensor, plan, wgt: torch.Tensor) -> None:
         """h[row] += sum_k wgt[row, k] * y[slot of (row, k)], float32, choices added in their order."""

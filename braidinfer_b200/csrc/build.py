@@ -32,7 +32,8 @@ CORE_SOURCES = ["errors.cu", "elementwise.cu", "pointwise.cu", "attn_simple.cu",
                 "fused_reduce.cu", "sampling.cu"]
 # Kernels that only some models use: each a library of its own, compiled when a model that needs it is built.
 PART_SOURCES = {"latent": ["errors.cu", "latent.cu"], "moe": ["errors.cu", "moe.cu"]}
-HEADERS = ["common.cuh", "rowscale.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h", "page.h", "trace.cuh"]
+HEADERS = ["common.cuh", "rowscale.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h", "page.h", "trace.cuh",
+           "mma_tile.cuh"]
 
 
 class BuildError(RuntimeError):
@@ -171,6 +172,12 @@ def part_library(name: str, verbose: bool = True) -> Path:
     if name not in PART_SOURCES:
         raise BuildError(f"no kernel library named {name!r}; known: {sorted(PART_SOURCES)}")
     return build_library(f"braidinfer_{name}", PART_SOURCES[name], verbose=verbose)
+
+
+def latent_attention_library(rank: int, rot: int, verbose: bool = True) -> Path:
+    """The tensor-core attention over a latent cache, compiled for one latent size (kv_rank, rot_dim)."""
+    return build_library(f"braidinfer_latattn_r{rank}_t{rot}", ["errors.cu", "latent_attn_mma.cu"],
+                         defines=[f"-DBRAID_LAT_RANK={rank}", f"-DBRAID_LAT_ROT={rot}"], verbose=verbose)
 
 
 def attention_library(head_dim: int, verbose: bool = True) -> Path:

@@ -13,6 +13,7 @@
 // write), a per-head matrix product, and one-warp-per-(token, head) attention over the latent cache.
 // Norm, angles, scores, softmax and accumulation are float32.
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 // ------------------------------------------------------------------ row preparation
 struct LatentPrepArgs {
@@ -190,6 +191,79 @@ extern "C" int braid_gemm_heads(const void* x, const void* w, void* out, const v
                      (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, n_rows, J, K, ldx, hsx,
                      ldo, hso, ldg, mult);
     else BRAID_REFUSE("gemm_heads: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// The same product in bfloat16 on the tensor cores (mma_tile.cuh): BM tokens x 64 outputs of one head a CTA.
+template <int BM>
+__global__ void __launch_bounds__(128)
+gemm_heads_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                      const __nv_bfloat16* __restrict__ gate, int n_rows, int J, int K, long long ldx, long long hsx,
+                      long long ldo, long long hso, long long ldg, float mult) {
+    using Tile = MmaTile<BM, 64, (BM >= 64 ? 2 : 1), (BM >= 64 ? 2 : 4), 1>;
+    extern __shared__ __align__(16) unsigned char hg_smem[];
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.z, n0 = blockIdx.y * BM, m0 = blockIdx.x * 64;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int ACH = BM * 4 / 128 > 0 ? BM * 4 / 128 : 1;
+    const __nv_bfloat16* a_rows[ACH];
+    const __nv_bfloat16* b_rows[1][2];
+#pragma unroll
+    for (int i = 0; i < ACH; ++i) {
+        const int r = (tid + i * 128) >> 2;
+        a_rows[i] = (r < BM && n0 + r < n_rows) ? x + (size_t)(n0 + r) * ldx + (size_t)h * hsx : nullptr;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int m = m0 + ((tid + i * 128) >> 2);
+        b_rows[0][i] = m < J ? w + ((size_t)h * J + m) * K : nullptr;
+    }
+    float acc[1][Tile::MI][Tile::NI][4];
+    Tile::run(acc, (__nv_bfloat16*)hg_smem, a_rows, b_rows, K, w);
+    const int wm0 = (warp / (BM >= 64 ? 2 : 4)) * (BM / (BM >= 64 ? 2 : 1)), wn0 = (warp % (BM >= 64 ? 2 : 4)) * (64 / (BM >= 64 ? 2 : 4));
+    const bool pairs_ok = ((ldo | hso) & 1) == 0;
+#pragma unroll
+    for (int mi = 0; mi < Tile::MI; ++mi)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int n = n0 + wm0 + mi * 16 + (lane >> 2) + half * 8;
+            if (n >= n_rows) continue;
+            float g = 1.f;
+            if (gate) g = mult / (1.f + expf(-__bfloat162float(gate[(size_t)n * ldg + h])));
+            __nv_bfloat16* orow = out + (size_t)n * ldo + (size_t)h * hso;
+#pragma unroll
+            for (int ni = 0; ni < Tile::NI; ++ni) {
+                const int col = m0 + wn0 + ni * 8 + 2 * (lane & 3);
+                const float v0 = acc[0][mi][ni][half * 2] * g, v1 = acc[0][mi][ni][half * 2 + 1] * g;
+                if (pairs_ok && col + 1 < J) *reinterpret_cast<__nv_bfloat162*>(orow + col) = __floats2bfloat162_rn(v0, v1);
+                else {
+                    if (col < J) orow[col] = __float2bfloat16_rn(v0);
+                    if (col + 1 < J) orow[col + 1] = __float2bfloat16_rn(v1);
+                }
+            }
+        }
+}
+
+extern "C" int braid_gemm_heads_mma(const void* x, const void* w, void* out, const void* gate, int n_rows, int heads,
+                                    int J, int K, long long ldx, long long hsx, long long ldo, long long hso,
+                                    long long ldg, float mult, void* stream) {
+    if (n_rows <= 0 || heads <= 0 || J <= 0) return BRAID_OK;
+    if (K <= 0 || K % 8 || ldx % 8 || hsx % 8) BRAID_REFUSE("gemm_heads_mma: k=%d and the strides %lld, %lld must be multiples of 8", K, ldx, hsx);
+    if (((uintptr_t)x | (uintptr_t)w) & 15) BRAID_REFUSE("gemm_heads_mma: operands must start on 16 bytes");
+    if (((uintptr_t)out & 3) != 0) BRAID_REFUSE("gemm_heads_mma: the output must start on 4 bytes");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int bm = n_rows <= 16 ? 16 : 64;
+    dim3 grid((J + 63) / 64, (n_rows + bm - 1) / bm, heads);
+    if (grid.y > 65535 || grid.z > 65535) BRAID_REFUSE("gemm_heads_mma: %d rows x %d heads exceed the grid limit", n_rows, heads);
+    if (bm == 16)
+        braid_launch(gemm_heads_mma_kernel<16>, grid, dim3(128), (size_t)MmaTile<16, 64, 1, 4, 1>::SMEM_BYTES, s,
+                     (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, n_rows, J, K,
+                     ldx, hsx, ldo, hso, ldg, mult);
+    else
+        braid_launch(gemm_heads_mma_kernel<64>, grid, dim3(128), (size_t)MmaTile<64, 64, 2, 2, 1>::SMEM_BYTES, s,
+                     (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, n_rows, J, K,
+                     ldx, hsx, ldo, hso, ldg, mult);
     BRAID_LAUNCH_CHECK();
 }
 

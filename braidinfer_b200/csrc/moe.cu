@@ -13,6 +13,7 @@
 // does not touch any number: every output row is a sum over k in a fixed order whatever its slot.
 // Launch sizes depend on the step's shape alone (an upper bound of tiles), so a CUDA graph can replay them.
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 // ------------------------------------------------------------------ routing
 struct MoeRouteArgs {
@@ -269,6 +270,104 @@ extern "C" int braid_moe_gemm_simt(const void* x, const void* w0, const void* w1
     else if (dtype == BRAID_BF16 && mode == 0) braid_launch(moe_gemm_simt_kernel<__nv_bfloat16, 0>, grid, dim3(256), 0, s, a);
     else if (dtype == BRAID_BF16 && mode == 1) braid_launch(moe_gemm_simt_kernel<__nv_bfloat16, 1>, grid, dim3(256), 0, s, a);
     else BRAID_REFUSE("moe_gemm: unknown dtype %d or mode %d", dtype, mode);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ the experts' products on the tensor cores
+// bfloat16, mma.sync with float32 accumulators (mma_tile.cuh).  One CTA a plan tile of BM slots (the plan's
+// tile is BM) and 64 outputs.  MODE 0 multiplies the gathered rows with the expert's gate and up matrices at
+// once and stores silu(gate) * up; MODE 1 multiplies the activations with the down matrix.
+template <int BM, int MODE>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(MoeGemmArgs a) {
+    constexpr int NB = MODE == 0 ? 2 : 1;
+    using Tile = MmaTile<BM, 64, (BM >= 64 ? 2 : 1), (BM >= 64 ? 2 : 4), NB>;
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y;
+    if (t >= a.meta[0]) return;
+    const int e = a.tile_expert[t];
+    const int slot0 = t * BM, m0 = blockIdx.x * 64;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int ACH = BM * 4 / 128 > 0 ? BM * 4 / 128 : 1;
+    const __nv_bfloat16* a_rows[ACH];
+    const __nv_bfloat16* b_rows[NB][2];
+    const __nv_bfloat16* x = (const __nv_bfloat16*)a.x;
+#pragma unroll
+    for (int i = 0; i < ACH; ++i) {
+        const int r = (tid + i * 128) >> 2;
+        a_rows[i] = nullptr;
+        if (r < BM) {
+            if (MODE == 0) {
+                const int pair = a.slot_pair[slot0 + r];
+                if (pair >= 0) a_rows[i] = x + (size_t)(pair / a.top) * a.ldx;
+            } else {
+                a_rows[i] = x + (size_t)(slot0 + r) * a.ldx;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int m = m0 + ((tid + i * 128) >> 2);
+        b_rows[0][i] = m < a.J ? (const __nv_bfloat16*)a.w0 + ((size_t)e * a.J + m) * a.K : nullptr;
+        if (MODE == 0) b_rows[NB - 1][i] = m < a.J ? (const __nv_bfloat16*)a.w1 + ((size_t)e * a.J + m) * a.K : nullptr;
+    }
+    float acc[NB][Tile::MI][Tile::NI][4];
+    Tile::run(acc, (__nv_bfloat16*)moe_smem, a_rows, b_rows, a.K, a.w0);
+    const int wm0 = (warp / (BM >= 64 ? 2 : 4)) * (BM / (BM >= 64 ? 2 : 1)), wn0 = (warp % (BM >= 64 ? 2 : 4)) * (64 / (BM >= 64 ? 2 : 4));
+    __nv_bfloat16* out = (__nv_bfloat16*)a.out;
+    const bool pairs_ok = (a.ldo & 1) == 0;
+#pragma unroll
+    for (int mi = 0; mi < Tile::MI; ++mi)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int slot = slot0 + wm0 + mi * 16 + (lane >> 2) + half * 8;
+            const bool live = MODE == 1 || a.slot_pair[slot] >= 0;
+#pragma unroll
+            for (int ni = 0; ni < Tile::NI; ++ni) {
+                const int col = m0 + wn0 + ni * 8 + 2 * (lane & 3);
+                float v0, v1;
+                if (MODE == 0) {
+                    const float g0 = acc[0][mi][ni][half * 2], g1 = acc[0][mi][ni][half * 2 + 1];
+                    v0 = live ? g0 / (1.f + expf(-g0)) * acc[NB - 1][mi][ni][half * 2] : 0.f;
+                    v1 = live ? g1 / (1.f + expf(-g1)) * acc[NB - 1][mi][ni][half * 2 + 1] : 0.f;
+                } else {
+                    v0 = acc[0][mi][ni][half * 2];
+                    v1 = acc[0][mi][ni][half * 2 + 1];
+                }
+                __nv_bfloat16* o = out + (size_t)slot * a.ldo + col;
+                if (pairs_ok && col + 1 < a.J) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(v0, v1);
+                else {
+                    if (col < a.J) o[0] = __float2bfloat16_rn(v0);
+                    if (col + 1 < a.J) o[1] = __float2bfloat16_rn(v1);
+                }
+            }
+        }
+}
+
+extern "C" int braid_moe_gemm_mma(const void* x, const void* w0, const void* w1, void* out, const int* slot_pair,
+                                  const int* tile_expert, const int* meta, int mode, long long ldx, long long ldo,
+                                  int J, int K, int top, int tile, int max_tiles, void* stream) {
+    if (max_tiles <= 0 || J <= 0) return BRAID_OK;
+    if (K <= 0 || K % 8 || ldx % 8) BRAID_REFUSE("moe_gemm_mma: k=%d and the row stride %lld must be multiples of 8", K, ldx);
+    if (((uintptr_t)x | (uintptr_t)w0 | (uintptr_t)w1) & 15) BRAID_REFUSE("moe_gemm_mma: operands must start on 16 bytes");
+    if (tile != 16 && tile != 64) BRAID_REFUSE("moe_gemm_mma: the plan's tile must be 16 or 64 slots, not %d", tile);
+    if (max_tiles > 65535) BRAID_REFUSE("moe_gemm_mma: %d tiles exceed the grid limit", max_tiles);
+    MoeGemmArgs a{x, w0, w1, out, slot_pair, tile_expert, meta, ldx, ldo, J, K, top, tile};
+    dim3 grid((J + 63) / 64, (unsigned)max_tiles);
+    cudaStream_t s = (cudaStream_t)stream;
+#define MOE_MMA(BM, MODE)                                                                                       \
+    do {                                                                                                        \
+        using T_ = MmaTile<BM, 64, (BM >= 64 ? 2 : 1), (BM >= 64 ? 2 : 4), (MODE == 0 ? 2 : 1)>;                \
+        braid_launch(moe_gemm_mma_kernel<BM, MODE>, grid, dim3(128), (size_t)T_::SMEM_BYTES, s, a);             \
+    } while (0)
+    if (tile == 64 && mode == 0) MOE_MMA(64, 0);
+    else if (tile == 64 && mode == 1) MOE_MMA(64, 1);
+    else if (tile == 16 && mode == 0) MOE_MMA(16, 0);
+    else if (tile == 16 && mode == 1) MOE_MMA(16, 1);
+    else BRAID_REFUSE("moe_gemm_mma: unknown mode %d", mode);
+#undef MOE_MMA
     BRAID_LAUNCH_CHECK();
 }
 

@@ -108,16 +108,34 @@ class LatentAttention(Mixer):
                       cache.page_table if writable else None, cache.storage if writable else None, q_lat,
                       self.heads, self.dim, self.rot, self.rank, self.pe.rope_dim, cache.page_size, self.eps)
         q_u = proj[:, :self.q_cols].view(rows, self.heads, self.dim + self.rot)[:, :, :self.dim]
-        K.gemm_heads(q_u, self.uk_t, q_lat[:, :, :self.rank])
+        tc = self.rt.gemm_backend == "auto"
+        K.gemm_heads(q_u, self.uk_t, q_lat[:, :, :self.rank], tensor_cores=tc)
         o_lat = self.rt.empty(rows, self.heads, self.rank)
         self._attend(q_lat, o_lat, ctx, cache)
         out = self.rt.empty(rows, self.heads * self.vdim)
         gate = proj[:, self.q_cols + self.D:self.q_cols + self.D + self.heads] if self.gated else None
         if gate is None and self.out_mult != 1.0:
             raise RuntimeError("latent_attention: an output factor needs the gate's epilogue")
-        K.gemm_heads(o_lat, self.uv, out.view(rows, self.heads, self.vdim), gate=gate, mult=self.out_mult)
+        K.gemm_heads(o_lat, self.uv, out.view(rows, self.heads, self.vdim), gate=gate, mult=self.out_mult, tensor_cores=tc)
         return self.o.forward(out, residual=residual, defer_to=ctx)
 
     def _attend(self, q_lat, o_lat, ctx, cache) -> None:
-        self.rt.kernels.attn_latent_simple(q_lat, o_lat, cache.storage, cache.page_table, ctx.positions, ctx.token_seq,
-                                           self.rank, self.window, self.scale)
+        """bfloat16 runs use the tensor-core kernel where it is built for the latent's size (prompts and decoding
+        alike; steps of few tokens slice the context so that a handful of sequences still fills the machine);
+        float32 runs, runs that ask for the plain kernels, and other sizes use one warp per (token, head)."""
+        K = self.rt.kernels
+        if self.rt.is_f32 or self.rt.attention_backend == "plain" or not K.attn_latent_mma_supports(self.rank, self.rot):
+            K.attn_latent_simple(q_lat, o_lat, cache.storage, cache.page_table, ctx.positions, ctx.token_seq,
+                                 self.rank, self.window, self.scale)
+            return
+        if ctx.rows > ctx.n_tokens:
+            o_lat.zero_()                                     # rows of padding are not written by the kernel
+        lib = K.latent_attention_library(self.rank, self.rot)
+        n_splits = 1
+        if ctx.max_q_len <= 8:
+            ctas = ctx.n_seqs * -(-ctx.max_q_len * self.heads // 64) * lib.vparts
+            span = min(ctx.max_kv_len, self.window) if self.window else ctx.max_kv_len
+            tiles = max(1, -(-span // 32))
+            n_splits = max(1, min(296 // ctas, tiles // 4, 32))      # two CTAs an SM, at least four key tiles a slice
+        K.attn_latent_mma(q_lat, o_lat, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before,
+                          ctx.token_seq, ctx.n_seqs, ctx.max_q_len, self.rank, self.window, self.scale, n_splits=n_splits)

@@ -89,6 +89,12 @@ class MixtureOfExperts(FeedForward):
         return residual
 
     def _experts(self, x, act, y, plan, tile) -> None:
+        """bfloat16 rows that start on 16 bytes run on the tensor cores, everything else on the plain kernels."""
         K = self.rt.kernels
+        tc = self.rt.gemm_backend == "auto"
+        if tc and K.moe_gemm_mma_eligible(x, self.w_gate, tile) and K.moe_gemm_mma_eligible(act, self.w_down, tile):
+            K.moe_gemm_mma(x, self.w_gate, self.w_up, act, plan, self.top, tile)
+            K.moe_gemm_mma(act, self.w_down, None, y, plan, self.top, tile)
+            return
         K.moe_gemm_simt(x, self.w_gate, self.w_up, act, plan, self.top, tile)
         K.moe_gemm_simt(act, self.w_down, None, y, plan, self.top, tile)

@@ -209,13 +209,29 @@ def paged(keys, dtype, ps=64, seed=0):
     return cache.cuda(), perm.to(torch.int32)[None, :].cuda()
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("far", [0, 3, 63, 64, 65, 127, 128, 640, 699])
-def test_one_far_key_that_stands_out_is_found_by_prompt_rows_and_by_a_decoded_token(K, dtype, far):
+def attend(K, kernel, q, out, cache, table, positions, rank, window, scale, n_splits=1):
+    """One sequence whose rows stand at consecutive `positions`, through the plain or the tensor-core kernel."""
+    rows = len(positions)
+    if kernel == "simple":
+        K.attn_latent_simple(q, out, cache, table, torch.tensor(positions, dtype=torch.int32).cuda(),
+                             torch.zeros(rows, dtype=torch.int32).cuda(), rank, window, scale)
+    else:
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+        K.attn_latent_mma(q, out, cache, table, i32([0]), i32([rows]), i32([positions[0]]), torch.zeros(rows, dtype=torch.int32).cuda(),
+                          1, rows, rank, window, scale, n_splits=n_splits)
+    K.check_device_errors()
+
+
+KERNELS = [("float32", "simple", 1), ("bfloat16", "simple", 1), ("bfloat16", "mma", 1), ("bfloat16", "mma", 4)]
+
+
+@pytest.mark.parametrize("dtype, kernel, n_splits", KERNELS)
+@pytest.mark.parametrize("far", [0, 3, 31, 32, 63, 64, 65, 127, 128, 640, 699])
+def test_one_far_key_that_stands_out_is_found_by_prompt_rows_and_by_a_decoded_token(K, dtype, kernel, n_splits, far):
     """Hundreds of keys with small scores and one, far back or at a page's edge, that every query points at:
     if it were missed the output would be another vector altogether."""
     g = torch.Generator().manual_seed(far)
-    T, heads, rank, rot = 700, 2, 24, 8
+    T, heads, rank, rot = (700, 2, 24, 8) if kernel == "simple" else (700, 5, 32, 16)
     D = rank + rot
     keys = torch.randn(T, D, generator=g) * 0.3
     u = torch.randn(D, generator=g)
@@ -227,9 +243,7 @@ def test_one_far_key_that_stands_out_is_found_by_prompt_rows_and_by_a_decoded_to
         rows = len(positions)
         q = (4.0 * u[None, None, :] + 0.2 * torch.randn(rows, heads, D, generator=g)).to(TORCH[dtype])
         out = torch.empty(rows, heads, rank, dtype=TORCH[dtype], device="cuda")
-        K.attn_latent_simple(q.cuda(), out, cache, table, torch.tensor(positions, dtype=torch.int32).cuda(),
-                             torch.zeros(rows, dtype=torch.int32).cuda(), rank, None, 0.5)
-        K.check_device_errors()
+        attend(K, kernel, q.cuda(), out, cache, table, positions, rank, None, 0.5, n_splits)
         want = plain_latent_mqa(q.double(), keys, positions, rank, 0.5)
         tol = 1e-5 if dtype == "float32" else 2e-2
         assert rel(out, want) < tol
@@ -237,15 +251,15 @@ def test_one_far_key_that_stands_out_is_found_by_prompt_rows_and_by_a_decoded_to
         assert rel(without, want) > 0.5                              # the test would see a missed key
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("window", [1, 2, 5, 64, 65, 200])
-def test_window_edges_just_inside_and_just_outside(K, dtype, window):
+@pytest.mark.parametrize("dtype, kernel, n_splits", KERNELS)
+@pytest.mark.parametrize("window", [1, 2, 5, 32, 33, 64, 65, 200])
+def test_window_edges_just_inside_and_just_outside(K, dtype, kernel, n_splits, window):
     g = torch.Generator().manual_seed(window)
-    T, heads, rank, rot = 300, 3, 16, 4
+    T, heads, rank, rot = (300, 3, 16, 4) if kernel == "simple" else (300, 3, 16, 16)
     D = rank + rot
     u = torch.randn(D, generator=g)
     u = u / u.norm()
-    for positions in ([299], [290, 291, 299]):
+    for positions in ([299], [297, 298, 299]):
         for edge in (0, 1):                                           # 0: the last key the window keeps; 1: the first it drops
             keys = torch.randn(T, D, generator=g) * 0.3
             j_star = positions[-1] - window + 1 - edge
@@ -255,12 +269,99 @@ def test_window_edges_just_inside_and_just_outside(K, dtype, window):
             rows = len(positions)
             q = (4.0 * u[None, None, :] + 0.2 * torch.randn(rows, heads, D, generator=g)).to(TORCH[dtype])
             out = torch.empty(rows, heads, rank, dtype=TORCH[dtype], device="cuda")
-            K.attn_latent_simple(q.cuda(), out, cache, table, torch.tensor(positions, dtype=torch.int32).cuda(),
-                                 torch.zeros(rows, dtype=torch.int32).cuda(), rank, window, 0.5)
+            attend(K, kernel, q.cuda(), out, cache, table, positions, rank, window, 0.5, n_splits)
             want = plain_latent_mqa(q.double(), keys, positions, rank, 0.5, window)
             assert rel(out, want) < (1e-5 if dtype == "float32" else 2e-2)
             hit = (out[-1, 0].double().cpu() - keys[j_star, :rank]).abs().max().item() < 0.5
             assert hit == (edge == 0)                                 # seen just inside, not seen just outside
+
+
+@pytest.mark.parametrize("n_splits", [1, 3])
+@pytest.mark.parametrize("rank, rot, heads", [(32, 16, 5), (48, 0, 2), (16, 32, 70)])
+def test_tensor_core_attention_on_a_batch_of_unequal_sequences(K, n_splits, rank, rot, heads):
+    """Prompts, a portion after a long context and a decoded token in one step, tiles that straddle tokens, rows
+    of padding, every sequence on pages of its own order: against float64 and against the plain kernel."""
+    g = torch.Generator().manual_seed(rank + heads)
+    D, ps = rank + rot, 64
+    before, q_len = [0, 100, 650, 63], [70, 1, 3, 2]
+    total = [b + n for b, n in zip(before, q_len)]
+    blocks = [-(-t // ps) for t in total]
+    pages = sum(blocks) + 2
+    order = torch.randperm(pages, generator=g).tolist()
+    cache = torch.zeros(pages, 1, 1, ps, D, dtype=torch.bfloat16)
+    table = torch.full((4, max(blocks)), -1, dtype=torch.int32)
+    keys = []
+    for s_, t in enumerate(total):
+        k = (torch.randn(t, D, generator=g) * 0.7).to(torch.bfloat16)
+        keys.append(k.double())
+        for b in range(blocks[s_]):
+            page = order.pop()
+            table[s_, b] = page
+            n = min(ps, t - b * ps)
+            cache[page, 0, 0, :n] = k[b * ps:b * ps + n]
+    rows = sum(q_len) + 4                                                  # four rows of padding
+    q = (torch.randn(rows, heads, D, generator=g) * 1.5).to(torch.bfloat16)
+    q_start = [sum(q_len[:i]) for i in range(4)]
+    token_seq = sum(([i] * n for i, n in enumerate(q_len)), []) + [-1] * 4
+    positions = sum((list(range(b, b + n)) for b, n in zip(before, q_len)), []) + [0] * 4
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    out = torch.full((rows, heads, rank), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.attn_latent_mma(q.cuda(), out, cache.cuda(), table.cuda(), i32(q_start), i32(q_len), i32(before), i32(token_seq),
+                      4, max(q_len), rank, None, 0.3, n_splits=n_splits)
+    twin = torch.empty_like(out)
+    K.attn_latent_simple(q.cuda(), twin, cache.cuda(), table.cuda(), i32(positions), i32(token_seq), rank, None, 0.3)
+    K.check_device_errors()
+    for s_ in range(4):
+        a, n = q_start[s_], q_len[s_]
+        want = plain_latent_mqa(q[a:a + n].double(), keys[s_], list(range(before[s_], before[s_] + n)), rank, 0.3)
+        assert rel(out[a:a + n], want) < 2e-2, s_
+        assert rel(out[a:a + n], twin[a:a + n].double().cpu()) < 2e-2, s_
+    assert (out[-4:] == 7.0).all()                                         # padding rows are left alone
+
+
+@pytest.mark.parametrize("rows", [5, 70])
+def test_tensor_core_per_head_products_against_the_plain_twin(K, rows):
+    g = torch.Generator().manual_seed(rows)
+    heads, k, j = 3, 24, 37
+    big = (torch.randn(rows, heads * (k + 8) + 8, generator=g)).to(torch.bfloat16).cuda()
+    x = big[:, :heads * (k + 8)].view(rows, heads, k + 8)[:, :, :k]
+    gate = big[:, heads * (k + 8):heads * (k + 8) + heads]
+    w = torch.randn(heads, j, k, generator=g).to(torch.bfloat16).cuda()
+    for gt in (None, gate):
+        out = torch.zeros(rows, heads, j + 1, dtype=torch.bfloat16, device="cuda")
+        twin = torch.zeros_like(out)
+        K.gemm_heads(x, w, out[:, :, :j], gate=gt, mult=0.7)
+        K.gemm_heads(x, w, twin[:, :, :j], gate=gt, mult=0.7, tensor_cores=False)
+        want = torch.einsum("nhk,hjk->nhj", x.cpu().double(), w.cpu().double())
+        if gt is not None:
+            want = want * 0.7 * torch.sigmoid(gt.cpu().double())[:, :, None]
+        assert rel(out[:, :, :j], want) < 1e-2 and rel(out, twin.double().cpu()) < 1e-2 and out[:, :, j:].abs().max() == 0
+
+
+@pytest.mark.parametrize("tile", [16, 64])
+def test_tensor_core_expert_products_against_the_plain_twin(K, tile):
+    g = torch.Generator().manual_seed(tile + 1)
+    rows, width, ff, experts, top = 150, 40, 72, 5, 2
+    x = torch.randn(rows, width, generator=g).to(torch.bfloat16).cuda()
+    wg, wu = [(torch.randn(experts, ff, width, generator=g) * 0.3).to(torch.bfloat16).cuda() for _ in range(2)]
+    wd = (torch.randn(experts, width, ff, generator=g) * 0.3).to(torch.bfloat16).cuda()
+    idx = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(rows)]).to(torch.int32)
+    idx[idx == 3] = 0                                                      # no row goes to expert 3
+    idx[:, 1][idx[:, 1] == idx[:, 0]] = 4
+    seq = torch.zeros(rows, dtype=torch.int32)
+    seq[-2:] = -1
+    plan = K.moe_plan(idx.cuda(), seq.cuda(), experts, tile)
+    slots = plan[4] * tile
+    res = []
+    for fn in (K.moe_gemm_mma, K.moe_gemm_simt):
+        act = torch.zeros(slots, ff, dtype=torch.bfloat16, device="cuda")
+        y = torch.zeros(slots, width, dtype=torch.bfloat16, device="cuda")
+        fn(x, wg, wu, act, plan, top, tile)
+        fn(act, wd, None, y, plan, top, tile)
+        res.append((act, y))
+    live = (plan[0] >= 0)
+    assert rel(res[0][0][live], res[1][0][live].double().cpu()) < 1e-2 and rel(res[0][1][live], res[1][1][live].double().cpu()) < 2e-2
+    assert res[0][0][~live[:slots]].abs().max() == 0                       # padding slots hold zeros
 
 
 @pytest.mark.parametrize("experts, groups, keep, top", [(6, 3, 2, 2), (5, 5, 3, 3), (64, 8, 4, 6), (4, 1, 1, 1), (8, 2, 1, 4),
