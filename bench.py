@@ -675,6 +675,217 @@ def run_chain(args):
     return 0
 
 
+# ------------------------------------------------------------------ the Bidinex decoder beside the dense one
+BIDINEX_SIZES = {
+    # name: width, heads, dim, rot_dim, vdim, kv_rank, experts, groups, keep, top, expert ff, layers, vocab
+    "w2048_e64": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, experts=64, groups=8, keep=4, top=6,
+                      ff=1408, layers=4, vocab=32768),
+    "w4096_e32": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, rank=512, experts=32, groups=4, keep=2, top=4,
+                      ff=2048, layers=4, vocab=32768),
+    "w1024_e16": dict(width=1024, heads=8, dim=64, rot=32, vdim=64, rank=256, experts=16, groups=1, keep=1, top=2,
+                      ff=1024, layers=4, vocab=32768),
+}
+
+
+def bidinex_config(z):
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "rot": {"base": 10000.0, "dims": z["rot"]},
+             "vdim": z["vdim"], "kv_rank": z["rank"], "scale": (z["dim"] + z["rot"]) ** -0.5}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    return {"architecture": "Bidinex", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "residual_mult": 1.0, "logit_softcap": 30.0,
+            "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": mlp} for _ in range(z["layers"])], "loop": None}
+
+
+def dense_twin_config(z):
+    """The dense decoder of equal size: same width, layers, heads and vocabulary, a head as large as a latent head's
+    query (dim + rot_dim, rounded to what the tcgen05 attention is built for), the feed-forward as wide as the
+    experts a token uses."""
+    hd = 128 if z["dim"] + z["rot"] > 64 else 64
+    return {"architectures": ["MistralForCausalLM"], "model_type": "mistral", "torch_dtype": "bfloat16",
+            "num_hidden_layers": z["layers"], "hidden_size": z["width"], "num_attention_heads": z["heads"],
+            "num_key_value_heads": max(1, z["heads"] // 4), "head_dim": hd, "intermediate_size": z["top"] * z["ff"],
+            "vocab_size": z["vocab"], "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "sliding_window": None,
+            "tie_word_embeddings": True, "max_position_embeddings": 32768}
+
+
+def run_bidinex(args):
+    """`--bidinex`: prompt and decode throughput of the Bidinex decoder at sizes like a real model's layers (random
+    weights, a few layers), beside the dense decoder of equal size, and the new kernels one by one beside the
+    dense model's like kernels with their fractions of the measured peaks.  Prints one JSON line of its own; the
+    default run and its line are untouched."""
+    import torch
+    from braidinfer_b200.engine import Engine
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, reps=5, warm=2, graph=False):
+        """Median device time of fn() after warm-up, L2 flushed before every call.  `graph`: fn's launches are
+        captured once and replayed, so that a kernel of a few microseconds is not timed by the host's launches."""
+        for _ in range(warm):
+            fn()
+        run = fn
+        if graph:
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                fn()
+            run = gr.replay
+            run()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / 1e3)
+        return statistics.median(ts)
+
+    def frac(seconds, flops, nbytes):
+        """Time the kernel's work takes at the measured peaks (the slower of its FLOPs and its bytes) over its time."""
+        return max(flops / (pk["bf16_tflops"] * 1e12), nbytes / (pk["hbm_gbs"] * 1e9)) / seconds
+
+    T, B, C = args.prompt_len, args.batch, args.context
+    sizes = [n for n in BIDINEX_SIZES if not args.sizes or n in args.sizes.split(",")]
+    out = {"metric": "bidinex_beside_dense_decoder", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic, random weights",
+           "prompt_len": T, "decode_batch": B, "decode_context": C, "peaks": pk, "l2": "flushed between timed calls",
+           "sizes": {}}
+    with ClockSampler() as clocks:
+        for name in sizes:
+            z = BIDINEX_SIZES[name]
+            row = {}
+            for label, cfg in (("bidinex", bidinex_config(z)), ("dense", dense_twin_config(z))):
+                eng = Engine.from_random(cfg, 1, dtype="bfloat16", on_device=True, max_tokens=max(B * (C + 192), T + 64),
+                                         max_slots=B, verbose=False)
+                g = torch.Generator().manual_seed(0)
+                prompt = torch.randint(0, z["vocab"], (T,), generator=g).tolist()
+
+                def prefill():
+                    s = eng.open()
+                    eng.step([(s, prompt)], want="last")
+                    eng.close(s)
+                tp = timed(prefill, reps=3, warm=2)
+                prompts = [torch.randint(0, z["vocab"], (C,), generator=g).tolist() for _ in range(B)]
+                secs, ctx0, launches = device_timed_decode(eng, eng.kernels, prompts, args.steps, max(args.warmup, 3))
+                eng.check()
+                row[label] = {"prefill_tokens_per_s": round(T / tp), "prefill_ms": round(tp * 1e3, 3),
+                              "decode_tokens_per_s": round(B * args.steps / secs), "decode_ms_per_step": round(secs / args.steps * 1e3, 4),
+                              "weight_gb": round(eng.weight_bytes / 1e9, 3), "launches_per_decode_step": launches // args.steps}
+                del eng
+                torch.cuda.empty_cache()
+            row["kernels"] = bidinex_kernels(z, T, B, C, timed, frac)
+            out["sizes"][name] = row
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
+def bidinex_kernels(z, T, B, C, timed, frac):
+    """The new kernels alone, each beside the dense decoder's like kernel: seconds, and the fraction of the measured
+    peak its algorithmic FLOPs or bytes (whichever bounds it) reach."""
+    import torch
+    from braidinfer_b200.cache import PAGE_SIZE
+    from braidinfer_b200.csrc.api import get_kernels
+    K = get_kernels(verbose=False)
+    dev, bf = "cuda", torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    H, R, rot, W, E, top, ff = z["heads"], z["rank"], z["rot"], z["width"], z["experts"], z["top"], z["ff"]
+    D = R + rot
+    hd = 128 if z["dim"] + z["rot"] > 64 else 64
+    nkh = max(1, H // 4)
+    res = {}
+
+    def paged(n_seqs, length, planes, heads, dim):
+        blocks = -(-length // PAGE_SIZE)
+        cache = torch.randn(n_seqs * blocks, planes, heads, PAGE_SIZE, dim, device=dev, dtype=bf) * 0.5
+        table = torch.arange(n_seqs * blocks, dtype=torch.int32, device=dev).view(n_seqs, blocks)
+        return cache, table
+
+    # ---- attention over a prompt of T tokens
+    cache, table = paged(1, T, 1, 1, D)
+    q = torch.randn(T, H, D, device=dev, dtype=bf) * 0.3
+    o = torch.empty(T, H, R, device=dev, dtype=bf)
+    seq0 = torch.zeros(T, dtype=torch.int32, device=dev)
+    z0, zT = i32([0]), i32([T])
+    t = timed(lambda: K.attn_latent_mma(q, o, cache, table, z0, zT, z0, seq0, 1, T, R, None, 0.1), graph=True)
+    fl = 2 * H * (D + R) * (T * (T + 1) // 2) * (2 if R > 256 else 1) / (2 if R > 256 else 1)
+    res["prompt_attention"] = {"latent_mma_ms": round(t * 1e3, 3), "latent_frac": round(frac(t, fl, 0), 3)}
+    dcache, dtable = paged(1, T, 2, nkh, hd)
+    qkv = torch.randn(T, (H + 2 * nkh) * hd, device=dev, dtype=bf) * 0.3
+    od = torch.empty(T, H * hd, device=dev, dtype=bf)
+    t = timed(lambda: K.attn_tc(qkv, od, dcache, dtable, z0, zT, z0, 1, T, H, nkh, hd, None, 0.1), graph=True)
+    res["prompt_attention"].update(dense_tcgen05_ms=round(t * 1e3, 3), dense_frac=round(frac(t, 2 * 2 * H * hd * (T * (T + 1) // 2), 0), 3))
+
+    # ---- attention of B decoded tokens over a context of C
+    cache, table = paged(B, C, 1, 1, D)
+    q = torch.randn(B, H, D, device=dev, dtype=bf) * 0.3
+    o = torch.empty(B, H, R, device=dev, dtype=bf)
+    seqs = torch.arange(B, dtype=torch.int32, device=dev)
+    ones, befores, starts = i32([1] * B), i32([C - 1] * B), i32(list(range(B)))
+    n_splits = max(1, min(296 // K.attn_latent_ctas(R, rot, B, 1, H), (C // 32) // 4, 32))
+    t = timed(lambda: K.attn_latent_mma(q, o, cache, table, starts, ones, befores, seqs, B, 1, R, None, 0.1, n_splits=n_splits), reps=9, graph=True)
+    res["decode_attention"] = {"latent_mma_ms": round(t * 1e3, 4), "latent_frac": round(frac(t, 0, B * C * D * 2), 3), "slices": n_splits}
+    dcache, dtable = paged(B, C, 2, nkh, hd)
+    qkv = torch.randn(B, (H + 2 * nkh) * hd, device=dev, dtype=bf) * 0.3
+    od = torch.empty(B, H * hd, device=dev, dtype=bf)
+    g = H // nkh
+    sp = max(1, min(K.attn_decode_slots(hd) // (B * nkh * -(-g // 16)), (C // 32) // 4, 64))
+    t = timed(lambda: K.attn_mma(qkv, od, dcache, dtable, starts, ones, befores, seqs, B, 1, H, nkh, hd, None, 0.1,
+                                 n_splits=sp, few_tokens=True), reps=9, graph=True)
+    res["decode_attention"].update(dense_mma_ms=round(t * 1e3, 4), dense_frac=round(frac(t, 0, B * C * 2 * nkh * hd * 2), 3))
+
+    # ---- the feed-forward's products: the experts over sorted rows beside the dense gate+up and down
+    for what, rows in (("prompt_experts", T), ("decode_experts", B)):
+        x = torch.randn(rows, W, device=dev, dtype=bf) * 0.3
+        wg, wu = [torch.randn(E, ff, W, device=dev, dtype=bf) * 0.02 for _ in range(2)]
+        wd = torch.randn(E, W, ff, device=dev, dtype=bf) * 0.02
+        idx = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(rows)]).to(torch.int32)
+        tile = 16 if rows * top <= 16 * E else 64
+        plan = K.moe_plan(idx, torch.zeros(rows, dtype=torch.int32, device=dev), E, tile)
+        act = torch.empty(plan[4] * tile, ff, device=dev, dtype=bf)
+        y = torch.empty(plan[4] * tile, W, device=dev, dtype=bf)
+        t1 = timed(lambda: K.moe_gemm_mma(x, wg, wu, act, plan, top, tile), graph=True)
+        t2 = timed(lambda: K.moe_gemm_mma(act, wd, None, y, plan, top, tile), graph=True)
+        used = int(torch.unique(idx).numel())
+        fl1, fl2 = 2 * rows * top * 2 * ff * W, 2 * rows * top * ff * W
+        by1, by2 = used * 2 * ff * W * 2, used * ff * W * 2
+        res[what] = {"gate_up_ms": round(t1 * 1e3, 4), "gate_up_frac": round(frac(t1, fl1, by1), 3),
+                     "down_ms": round(t2 * 1e3, 4), "down_frac": round(frac(t2, fl2, by2), 3), "experts_used": used, "tile": tile}
+        del wg, wu, wd
+        I = top * ff
+        from braidinfer_b200.csrc.api import interleave_gate_up
+        from braidinfer_b200.parts.linear import stream_k_pays
+        wgu = interleave_gate_up(torch.randn(I, W, device=dev, dtype=bf) * 0.02, torch.randn(I, W, device=dev, dtype=bf) * 0.02)
+        wdn = torch.randn(W, I, device=dev, dtype=bf) * 0.02
+        a2 = torch.empty(rows, I, device=dev, dtype=bf)
+        hres = torch.zeros(rows, W, device=dev, dtype=torch.float32)
+        sk1, sk2 = stream_k_pays(rows, wgu.shape[0], W), stream_k_pays(rows, W, I)
+        t1 = timed(lambda: K.gemm_tc(x, wgu, a2, swiglu=True, stream_k=sk1), graph=True)
+        t2 = timed(lambda: K.gemm_tc(a2, wdn, hres, residual=hres, stream_k=sk2), graph=True)
+        res[what].update(dense_gate_up_ms=round(t1 * 1e3, 4), dense_gate_up_frac=round(frac(t1, 2 * rows * 2 * I * W, 2 * I * W * 2), 3),
+                         dense_down_ms=round(t2 * 1e3, 4), dense_down_frac=round(frac(t2, 2 * rows * I * W, I * W * 2), 3))
+        del wgu, wdn
+    # ---- the per-head products of the latent mixer (no like kernel in the dense decoder)
+    for what, rows in (("prompt_head_products", T), ("decode_head_products", B)):
+        qx = torch.randn(rows, H, z["dim"] + rot, device=dev, dtype=bf)[:, :, :z["dim"]]
+        wk = torch.randn(H, R, z["dim"], device=dev, dtype=bf) * 0.05
+        ql = torch.empty(rows, H, D, device=dev, dtype=bf)
+        qlv = ql[:, :, :R]
+        t1 = timed(lambda: K.gemm_heads(qx, wk, qlv), graph=True)
+        ol = torch.randn(rows, H, R, device=dev, dtype=bf)
+        wv = torch.randn(H, z["vdim"], R, device=dev, dtype=bf) * 0.05
+        ov = torch.empty(rows, H, z["vdim"], device=dev, dtype=bf)
+        t2 = timed(lambda: K.gemm_heads(ol, wv, ov), graph=True)
+        res[what] = {"into_latent_ms": round(t1 * 1e3, 4),
+                     "into_latent_frac": round(frac(t1, 2 * rows * H * R * z["dim"], 2 * (rows * H * (z["dim"] + R) + H * R * z["dim"])), 3),
+                     "out_of_latent_ms": round(t2 * 1e3, 4),
+                     "out_of_latent_frac": round(frac(t2, 2 * rows * H * R * z["vdim"], 2 * (rows * H * (z["vdim"] + R) + H * R * z["vdim"])), 3)}
+    return res
+
+
 def run_reference(args):
     print(json.dumps({"impl": "reference", "unavailable":
                       "mcelrath/braidinfer is Rust + HIP for AMD RDNA3: pip finds neither setup.py nor pyproject.toml, "
@@ -707,12 +918,20 @@ def main() -> int:
                          "(see run_prompt_timeline)")
     ap.add_argument("--timeline", action="store_true",
                     help="one decode step under the torch profiler: a layer's kernels with their share (see run_timeline)")
+    ap.add_argument("--bidinex", action="store_true",
+                    help="the Bidinex decoder at sizes like a real model's layers beside the dense decoder of equal size, "
+                         "and its kernels one by one; prints its own line (see run_bidinex)")
+    ap.add_argument("--sizes", default="", help="with --bidinex: names of BIDINEX_SIZES, with commas (default: all)")
+    ap.add_argument("--prompt-len", type=int, default=2048, help="with --bidinex: tokens of the timed prompt")
+    ap.add_argument("--context", type=int, default=2048, help="with --bidinex: context of the timed decode steps")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.bidinex:
+        return run_bidinex(args)
     if args.sweep:
         return run_sweep(args)
     if args.prompt_timeline:

@@ -603,10 +603,20 @@ class Kernels:
             lib.braid_latent_attn_partial_floats.restype = c_longlong
             lib.braid_latent_attn_partial_floats.argtypes = [c_int, c_int, c_int]
             lib.vparts = lib.braid_latent_attn_vparts()
+            lib.braid_latent_attn_tile_rows.restype = c_int
+            lib.braid_latent_attn_tile_rows.argtypes = [c_int, c_int]
             if (lib.braid_latent_attn_rank(), lib.braid_latent_attn_rot()) != (rank, rot):
                 raise KernelError("the latent attention library was built for another size")
             self._part_libs[key] = lib
         return lib
+
+    def attn_latent_ctas(self, rank: int, rot: int, n_seqs: int, max_q_len: int, heads: int) -> int:
+        """CTAs of the tensor-core latent attention for a step, before the context is sliced: steps of few
+        (token, head) pairs run tiles of 16 rows whose warps share the rows, others tiles of 64 (and, for a
+        rank above 256, one CTA a part of 256 value columns)."""
+        lib = self.latent_attention_library(rank, rot)
+        tile = lib.braid_latent_attn_tile_rows(max_q_len, heads)
+        return n_seqs * -(-max_q_len * heads // tile) * (1 if tile == 16 else lib.vparts)
 
     def attn_latent_mma(self, q_lat: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
                         q_start: torch.Tensor, q_len: torch.Tensor, kv_before: torch.Tensor, token_seq: torch.Tensor,

@@ -230,6 +230,202 @@ latent_attn_mma_kernel(LatAttnArgs a) {
     }
 }
 
+// ------------------------------------------------------------------ steps of few (token, head) pairs
+// A decoded token of a model with few heads fills one m16 tile at most, so the four warps of a CTA share the same
+// sixteen rows instead of taking sixteen each: they split the scores' sum over the D numbers of a key (warp w takes
+// every fourth block of 16; partial scores meet in shared memory), every warp then holds all scores, runs the same
+// softmax, and accumulates its own quarter of the value columns.  No product is computed twice, and a rank above 256
+// needs no column parts.  Built where kv_rank is a multiple of 64.
+namespace {
+constexpr bool FEW_OK = (R % 64 == 0);
+constexpr int VQ = FEW_OK ? R / 4 : 16;
+constexpr int FEW_ROWS = 16;
+constexpr int SP_LD = BN + 1;
+constexpr int SMEM_FEW = (FEW_ROWS + 2 * BN) * LDK * 2 + 2 * 4 * FEW_ROWS * SP_LD * 4;
+}
+
+__global__ void __launch_bounds__(128)
+latent_attn_few_kernel(LatAttnArgs a) {
+    extern __shared__ __align__(16) unsigned char lat_smem[];
+    __nv_bfloat16* Qs = (__nv_bfloat16*)lat_smem;
+    __nv_bfloat16* Ks = Qs + FEW_ROWS * LDK;
+    float* Sp = (float*)(Ks + 2 * BN * LDK);             // [2][4 warps][16][SP_LD]
+    pdl_trigger();
+    pdl_wait();
+    const int seq = blockIdx.y, split = blockIdx.z;
+    const int pairs = a.q_len[seq] * a.heads;
+    const int pair0 = blockIdx.x * FEW_ROWS;
+    if (pair0 >= pairs) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int before = a.kv_before[seq];
+    const long long base_pair = (long long)a.q_start[seq] * a.heads + pair0;
+    const int n_here = min(FEW_ROWS, pairs - pair0);
+    const int t_first = pair0 / a.heads, t_last = (pair0 + n_here - 1) / a.heads;
+    const int hi = before + t_last;
+    int lo = 0;
+    if (a.window > 0 && before + t_first - a.window + 1 > 0) lo = before + t_first - a.window + 1;
+    const int tile_lo = lo / BN, tile_hi = hi / BN;
+    const int per = (tile_hi - tile_lo + 1 + a.n_splits - 1) / a.n_splits;
+    const int my_lo = tile_lo + split * per;
+    const int my_hi = min(tile_hi, my_lo + per - 1);
+    constexpr int CH = D / 8;
+    {
+        const __nv_bfloat16* src = a.q + base_pair * D;
+        for (int c = tid; c < FEW_ROWS * CH; c += 128) {
+            const int r = c / CH, kc = (c - r * CH) * 8;
+            const bool ok = r < n_here;
+            mt_cp_async16(Qs + r * LDK + kc, ok ? src + (size_t)r * D + kc : a.q, ok ? 16 : 0);
+        }
+    }
+    const int* table = a.page_table + (size_t)seq * a.table_cols;
+    auto load_keys = [&](int tile, int stage) {
+        const int j0 = tile * BN;
+        const int block = j0 / BRAID_PAGE_SIZE, off = j0 - block * BRAID_PAGE_SIZE;
+        int page = (block < a.table_cols) ? table[block] : -1;
+        if (page < 0 || page >= a.num_pages) {
+            if (tid == 0) atomicExch(a.error_flag, 1);
+            page = 0;
+        }
+        const __nv_bfloat16* src = a.cache + ((size_t)page * BRAID_PAGE_SIZE + off) * D;
+        __nv_bfloat16* dst = Ks + stage * BN * LDK;
+        for (int c = tid; c < BN * CH; c += 128) {
+            const int r = c / CH, kc = (c - r * CH) * 8;
+            mt_cp_async16(dst + r * LDK + kc, src + (size_t)r * D + kc, 16);
+        }
+    };
+    if (my_lo <= my_hi) load_keys(my_lo, 0);
+    mt_commit();
+    const int g = lane >> 2, qd = lane & 3;
+    int pos_row[2];
+    bool live_row[2];
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+        const int idx = g + h2 * 8;
+        live_row[h2] = idx < n_here;
+        pos_row[h2] = before + (pair0 + idx) / a.heads;
+    }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float oacc[VQ / 8][4];
+#pragma unroll
+    for (int i = 0; i < VQ / 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[i][e] = 0.f;
+    for (int tile = my_lo; tile <= my_hi; ++tile) {
+        const int it = tile - my_lo, stage = it & 1;
+        if (tile + 1 <= my_hi) {
+            load_keys(tile + 1, stage ^ 1);
+            mt_commit();
+            mt_wait<1>();
+        } else {
+            mt_wait<0>();
+        }
+        __syncthreads();
+        const __nv_bfloat16* Kt = Ks + stage * BN * LDK;
+        float sacc[BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sacc[i][e] = 0.f;
+        for (int kd = warp; kd < D / 16; kd += 4) {
+            unsigned af[4];
+            mt_ldmatrix_x4(af, Qs + (lane & 15) * LDK + kd * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int np = 0; np < BN / 16; ++np) {
+                unsigned bf[4];
+                mt_ldmatrix_x4(bf, Kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * LDK + kd * 16 + ((lane >> 3) & 1) * 8);
+                mt_mma(sacc[2 * np], af, bf[0], bf[1]);
+                mt_mma(sacc[2 * np + 1], af, bf[2], bf[3]);
+            }
+        }
+        float* mine = Sp + ((it & 1) * 4 + warp) * FEW_ROWS * SP_LD;
+#pragma unroll
+        for (int ni = 0; ni < BN / 8; ++ni)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) mine[(g + (e >> 1) * 8) * SP_LD + ni * 8 + 2 * qd + (e & 1)] = sacc[ni][e];
+        __syncthreads();
+        const float* all = Sp + (it & 1) * 4 * FEW_ROWS * SP_LD;
+        const int j0 = tile * BN;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int ni = 0; ni < BN / 8; ++ni)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h2 = e >> 1;
+                const int o = (g + h2 * 8) * SP_LD + ni * 8 + 2 * qd + (e & 1);
+                const float dot = (all[o] + all[FEW_ROWS * SP_LD + o]) + (all[2 * FEW_ROWS * SP_LD + o] + all[3 * FEW_ROWS * SP_LD + o]);
+                const int j = j0 + ni * 8 + 2 * qd + (e & 1);
+                const bool vis = live_row[h2] && j <= pos_row[h2] && (a.window <= 0 || pos_row[h2] - j < a.window);
+                const float s = vis ? dot * a.scale_log2 : -INFINITY;
+                sacc[ni][e] = s;
+                mx[h2] = fmaxf(mx[h2], s);
+            }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 1));
+            mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 2));
+            const float m_new = fmaxf(m_run[h2], mx[h2]);
+            m_use[h2] = (m_new == -INFINITY) ? 0.f : m_new;
+            corr[h2] = exp2f(m_run[h2] - m_use[h2]);
+            m_run[h2] = m_new;
+            l_run[h2] *= corr[h2];
+        }
+        unsigned pf[BN / 16][4];
+#pragma unroll
+        for (int ni = 0; ni < BN / 8; ++ni) {
+            const float p0 = exp2f(sacc[ni][0] - m_use[0]), p1 = exp2f(sacc[ni][1] - m_use[0]);
+            const float p2 = exp2f(sacc[ni][2] - m_use[1]), p3 = exp2f(sacc[ni][3] - m_use[1]);
+            l_run[0] += p0 + p1;
+            l_run[1] += p2 + p3;
+            __nv_bfloat162 lo2 = __floats2bfloat162_rn(p0, p1), hi2 = __floats2bfloat162_rn(p2, p3);
+            pf[ni >> 1][(ni & 1) * 2] = *reinterpret_cast<unsigned*>(&lo2);
+            pf[ni >> 1][(ni & 1) * 2 + 1] = *reinterpret_cast<unsigned*>(&hi2);
+        }
+#pragma unroll
+        for (int i = 0; i < VQ / 8; ++i) {
+            oacc[i][0] *= corr[0]; oacc[i][1] *= corr[0];
+            oacc[i][2] *= corr[1]; oacc[i][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+#pragma unroll
+            for (int np = 0; np < VQ / 16; ++np) {
+                unsigned bf[4];
+                mt_ldmatrix_x4_trans(bf, Kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + warp * VQ + np * 16 + (lane >> 4) * 8);
+                mt_mma(oacc[2 * np], pf[kk], bf[0], bf[1]);
+                mt_mma(oacc[2 * np + 1], pf[kk], bf[2], bf[3]);
+            }
+        __syncthreads();
+    }
+    if (my_lo > my_hi) mt_wait<0>();
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+        l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 1);
+        l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 2);
+    }
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+        if (!live_row[h2]) continue;
+        const long long pair = base_pair + g + h2 * 8;
+        if (a.partial == nullptr) {
+            const float inv = 1.f / l_run[h2];
+            __nv_bfloat16* o = a.out + pair * R + warp * VQ;
+#pragma unroll
+            for (int i = 0; i < VQ / 8; ++i)
+                *reinterpret_cast<__nv_bfloat162*>(o + i * 8 + 2 * qd) = __floats2bfloat162_rn(oacc[i][h2 * 2] * inv, oacc[i][h2 * 2 + 1] * inv);
+        } else {
+            float* o = a.partial + ((size_t)split * a.total_pairs + pair) * (R + 2);
+#pragma unroll
+            for (int i = 0; i < VQ / 8; ++i)
+                *reinterpret_cast<float2*>(o + warp * VQ + i * 8 + 2 * qd) = make_float2(oacc[i][h2 * 2], oacc[i][h2 * 2 + 1]);
+            if (qd == 0 && warp == 0) {
+                o[R] = m_run[h2];
+                o[R + 1] = l_run[h2];
+            }
+        }
+    }
+}
+
 // Merge of the context's slices: out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s, M = max_s m_s.
 __global__ void __launch_bounds__(128)
 latent_attn_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, const int* __restrict__ token_seq,
@@ -260,6 +456,11 @@ extern "C" int braid_latent_attn_rank(void) { return R; }
 extern "C" int braid_latent_attn_rot(void) { return RT; }
 extern "C" int braid_latent_attn_vparts(void) { return VPARTS; }
 
+// Rows of a CTA's tile for a step whose sequences bring up to max_q_len tokens: 16 (the kernel for few pairs) or 64.
+extern "C" int braid_latent_attn_tile_rows(int max_q_len, int heads) {
+    return (FEW_OK && (long long)max_q_len * heads <= 32) ? FEW_ROWS : BM;
+}
+
 extern "C" long long braid_latent_attn_partial_floats(int rows, int heads, int n_splits) {
     return (long long)n_splits * rows * heads * (R + 2);
 }
@@ -276,11 +477,14 @@ extern "C" int braid_latent_attn_mma(const void* q, void* out, float* partial, c
     if (heads <= 0 || table_cols <= 0 || num_pages <= 0) BRAID_REFUSE("latent_attn_mma: heads=%d, table columns=%d, pages=%d", heads, table_cols, num_pages);
     if (n_splits < 1 || (n_splits > 1 && !partial)) BRAID_REFUSE("latent_attn_mma: %d slices need a workspace", n_splits);
     if (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15) BRAID_REFUSE("latent_attn_mma: operands must start on 16 bytes");
-    const long long tiles = ((long long)max_q_len * heads + BM - 1) / BM;
+    const bool few = braid_latent_attn_tile_rows(max_q_len, heads) == FEW_ROWS;
+    const int tile_rows = few ? FEW_ROWS : BM;
+    const long long tiles = ((long long)max_q_len * heads + tile_rows - 1) / tile_rows;
     if (tiles > 0x7fffffffLL || n_seqs > 65535 || n_splits * VPARTS > 65535) BRAID_REFUSE("latent_attn_mma: the step exceeds one launch");
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess && FEW_OK) e = cudaFuncSetAttribute(latent_attn_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_FEW);
         if (e != cudaSuccess) BRAID_REFUSE("latent_attn_mma: %d bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(e));
         attr_set = true;
     }
@@ -288,8 +492,9 @@ extern "C" int braid_latent_attn_mma(const void* q, void* out, float* partial, c
                   page_table, q_start, q_len, kv_before, heads, table_cols, num_pages, window, n_splits, rows * heads,
                   scale * 1.4426950408889634f, error_flag};
     cudaStream_t s = (cudaStream_t)stream;
-    cudaError_t e = braid_launch(latent_attn_mma_kernel, dim3((unsigned)tiles, n_seqs, n_splits * VPARTS), dim3(128),
-                                 (size_t)SMEM_BYTES, s, a);
+    cudaError_t e = few
+        ? braid_launch(latent_attn_few_kernel, dim3((unsigned)tiles, n_seqs, n_splits), dim3(128), (size_t)SMEM_FEW, s, a)
+        : braid_launch(latent_attn_mma_kernel, dim3((unsigned)tiles, n_seqs, n_splits * VPARTS), dim3(128), (size_t)SMEM_BYTES, s, a);
     if (e == cudaSuccess && n_splits > 1)
         braid_launch(latent_attn_merge_kernel, dim3(rows * heads), dim3(128), 0, s, (const float*)partial, (__nv_bfloat16*)out,
                      token_seq, heads, rows * heads, n_splits);

@@ -90,13 +90,17 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time (the cache is sized for them, plus a page of "
+                         "slack for each of up to 512 live requests, whose last pages are part empty)")
     ap.add_argument("--dump-activations", metavar="DIR", default=None,
                     help="also write the residual stream after the embedding and after every run of a layer, "
                          "DIR/<step>.act.f32 = float32 [1 + runs, tokens of the step, width]")
     a = ap.parse_args(argv)
+    from ..cache import PAGE_SIZE
     from .engine import Engine
-    engine = Engine.from_folder(a.model, dtype=a.dtype, max_tokens=a.max_tokens, verbose=True)
+    # every live request may leave its last page part empty: a page of slack for each request there can be
+    slack = PAGE_SIZE * max(1, min(512, a.max_tokens))
+    engine = Engine.from_folder(a.model, dtype=a.dtype, max_tokens=a.max_tokens + slack, verbose=True)
 
     def say(msg: str) -> None:
         sys.stdout.write(msg + "\n")

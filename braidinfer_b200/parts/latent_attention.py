@@ -130,10 +130,9 @@ class LatentAttention(Mixer):
             return
         if ctx.rows > ctx.n_tokens:
             o_lat.zero_()                                     # rows of padding are not written by the kernel
-        lib = K.latent_attention_library(self.rank, self.rot)
         n_splits = 1
         if ctx.max_q_len <= 8:
-            ctas = ctx.n_seqs * -(-ctx.max_q_len * self.heads // 64) * lib.vparts
+            ctas = K.attn_latent_ctas(self.rank, self.rot, ctx.n_seqs, ctx.max_q_len, self.heads)
             span = min(ctx.max_kv_len, self.window) if self.window else ctx.max_kv_len
             tiles = max(1, -(-span // 32))
             n_splits = max(1, min(296 // ctas, tiles // 4, 32))      # two CTAs an SM, at least four key tiles a slice

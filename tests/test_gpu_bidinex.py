@@ -222,7 +222,9 @@ def attend(K, kernel, q, out, cache, table, positions, rank, window, scale, n_sp
     K.check_device_errors()
 
 
-KERNELS = [("float32", "simple", 1), ("bfloat16", "simple", 1), ("bfloat16", "mma", 1), ("bfloat16", "mma", 4)]
+# "mma64": a latent whose rank is a multiple of 64 and few heads, so that a decoded token runs the kernel for few pairs
+KERNELS = [("float32", "simple", 1), ("bfloat16", "simple", 1), ("bfloat16", "mma", 1), ("bfloat16", "mma", 4),
+           ("bfloat16", "mma64", 1), ("bfloat16", "mma64", 5)]
 
 
 @pytest.mark.parametrize("dtype, kernel, n_splits", KERNELS)
@@ -231,7 +233,7 @@ def test_one_far_key_that_stands_out_is_found_by_prompt_rows_and_by_a_decoded_to
     """Hundreds of keys with small scores and one, far back or at a page's edge, that every query points at:
     if it were missed the output would be another vector altogether."""
     g = torch.Generator().manual_seed(far)
-    T, heads, rank, rot = (700, 2, 24, 8) if kernel == "simple" else (700, 5, 32, 16)
+    T, heads, rank, rot = {"simple": (700, 2, 24, 8), "mma": (700, 5, 32, 16), "mma64": (700, 3, 64, 16)}[kernel]
     D = rank + rot
     keys = torch.randn(T, D, generator=g) * 0.3
     u = torch.randn(D, generator=g)
@@ -255,7 +257,7 @@ def test_one_far_key_that_stands_out_is_found_by_prompt_rows_and_by_a_decoded_to
 @pytest.mark.parametrize("window", [1, 2, 5, 32, 33, 64, 65, 200])
 def test_window_edges_just_inside_and_just_outside(K, dtype, kernel, n_splits, window):
     g = torch.Generator().manual_seed(window)
-    T, heads, rank, rot = (300, 3, 16, 4) if kernel == "simple" else (300, 3, 16, 16)
+    T, heads, rank, rot = {"simple": (300, 3, 16, 4), "mma": (300, 3, 16, 16), "mma64": (300, 2, 128, 0)}[kernel]
     D = rank + rot
     u = torch.randn(D, generator=g)
     u = u / u.norm()
@@ -274,6 +276,47 @@ def test_window_edges_just_inside_and_just_outside(K, dtype, kernel, n_splits, w
             assert rel(out, want) < (1e-5 if dtype == "float32" else 2e-2)
             hit = (out[-1, 0].double().cpu() - keys[j_star, :rank]).abs().max().item() < 0.5
             assert hit == (edge == 0)                                 # seen just inside, not seen just outside
+
+
+@pytest.mark.parametrize("n_splits", [1, 6])
+@pytest.mark.parametrize("rank, rot, heads, n_seqs", [(64, 16, 4, 5), (192, 32, 16, 3), (256, 0, 1, 9)])
+def test_decoded_tokens_of_few_heads_share_a_tile_among_the_warps(K, n_splits, rank, rot, heads, n_seqs):
+    """One token a sequence (and one sequence with two), contexts that end at, before and after page borders."""
+    g = torch.Generator().manual_seed(rank + heads)
+    D, ps = rank + rot, 64
+    before = [0, 63, 64, 130, 700, 31, 32, 1, 255][:n_seqs]
+    q_len = [1] * n_seqs
+    q_len[-1] = 2 if heads * 2 <= 32 else 1
+    total = [b + n for b, n in zip(before, q_len)]
+    blocks = [-(-t // ps) for t in total]
+    order = torch.randperm(sum(blocks) + 1, generator=g).tolist()
+    cache = torch.zeros(sum(blocks) + 1, 1, 1, ps, D, dtype=torch.bfloat16)
+    table = torch.full((n_seqs, max(blocks)), -1, dtype=torch.int32)
+    keys = []
+    for s_, t in enumerate(total):
+        k = (torch.randn(t, D, generator=g) * 0.7).to(torch.bfloat16)
+        keys.append(k.double())
+        for b in range(blocks[s_]):
+            page = order.pop()
+            table[s_, b] = page
+            n = min(ps, t - b * ps)
+            cache[page, 0, 0, :n] = k[b * ps:b * ps + n]
+    rows = sum(q_len) + 2
+    q = (torch.randn(rows, heads, D, generator=g) * 1.0).to(torch.bfloat16)
+    q_start = [sum(q_len[:i]) for i in range(n_seqs)]
+    token_seq = sum(([i] * n for i, n in enumerate(q_len)), []) + [-1] * 2
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    lib = K.latent_attention_library(rank, rot)
+    assert lib.braid_latent_attn_tile_rows(max(q_len), heads) == 16
+    out = torch.full((rows, heads, rank), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.attn_latent_mma(q.cuda(), out, cache.cuda(), table.cuda(), i32(q_start), i32(q_len), i32(before), i32(token_seq),
+                      n_seqs, max(q_len), rank, None, 0.2, n_splits=n_splits)
+    K.check_device_errors()
+    for s_ in range(n_seqs):
+        a, n = q_start[s_], q_len[s_]
+        want = plain_latent_mqa(q[a:a + n].double(), keys[s_], list(range(before[s_], before[s_] + n)), rank, 0.2)
+        assert rel(out[a:a + n], want) < 2e-2, s_
+    assert (out[-2:] == 7.0).all()
 
 
 @pytest.mark.parametrize("n_splits", [1, 3])
