@@ -32,7 +32,7 @@ static_assert(BRAID_PAGE_SIZE % BN == 0, "a key tile lies within one page");
 struct LatAttnArgs {
     const __nv_bfloat16* q;        // [rows, heads, D] contiguous
     __nv_bfloat16* out;            // [rows, heads, R] contiguous
-    float* partial;                // slices: [n_splits][rows * heads][R + 2], else null
+    float* partial;                // slices: [n_splits][rows * heads][R + 4], else null
     const __nv_bfloat16* cache;    // [pages][page_size][D]
     const int* page_table;         // [n_seqs, table_cols]
     const int* q_start;
@@ -218,7 +218,7 @@ latent_attn_mma_kernel(LatAttnArgs a) {
             for (int i = 0; i < VC / 8; ++i)
                 *reinterpret_cast<__nv_bfloat162*>(o + i * 8 + 2 * qd) = __floats2bfloat162_rn(oacc[i][h2 * 2] * inv, oacc[i][h2 * 2 + 1] * inv);
         } else {
-            float* o = a.partial + ((size_t)split * a.total_pairs + pair) * (R + 2);
+            float* o = a.partial + ((size_t)split * a.total_pairs + pair) * (R + 4);
 #pragma unroll
             for (int i = 0; i < VC / 8; ++i)
                 *reinterpret_cast<float2*>(o + vc0 + i * 8 + 2 * qd) = make_float2(oacc[i][h2 * 2], oacc[i][h2 * 2 + 1]);
@@ -414,7 +414,7 @@ latent_attn_few_kernel(LatAttnArgs a) {
             for (int i = 0; i < VQ / 8; ++i)
                 *reinterpret_cast<__nv_bfloat162*>(o + i * 8 + 2 * qd) = __floats2bfloat162_rn(oacc[i][h2 * 2] * inv, oacc[i][h2 * 2 + 1] * inv);
         } else {
-            float* o = a.partial + ((size_t)split * a.total_pairs + pair) * (R + 2);
+            float* o = a.partial + ((size_t)split * a.total_pairs + pair) * (R + 4);
 #pragma unroll
             for (int i = 0; i < VQ / 8; ++i)
                 *reinterpret_cast<float2*>(o + warp * VQ + i * 8 + 2 * qd) = make_float2(oacc[i][h2 * 2], oacc[i][h2 * 2 + 1]);
@@ -426,29 +426,56 @@ latent_attn_few_kernel(LatAttnArgs a) {
     }
 }
 
-// Merge of the context's slices: out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s, M = max_s m_s.
+// Merge of the context's slices: out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s, M = max_s m_s.  One CTA a
+// (token, head) pair: the slices' (max, sum) pairs are fetched once into shared memory, then every thread adds up
+// four columns over the slices with all its loads in flight at once (up to 64 slices).
+#define LAT_MERGE_MAX_SPLITS 64
 __global__ void __launch_bounds__(128)
 latent_attn_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, const int* __restrict__ token_seq,
                          int heads, int total_pairs, int n_splits) {
     pdl_trigger();
     pdl_wait();
+    __shared__ float wgt[LAT_MERGE_MAX_SPLITS];
+    __shared__ float inv_s;
     const int pair = blockIdx.x;
     if (token_seq[pair / heads] < 0) return;             // a padding row: nothing was computed for it
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, partial[((size_t)s * total_pairs + pair) * (R + 2) + R]);
-    float denom = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float* p = partial + ((size_t)s * total_pairs + pair) * (R + 2);
-        denom += (p[R] == -INFINITY) ? 0.f : exp2f(p[R] - M) * p[R + 1];
-    }
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    for (int c = threadIdx.x; c < R; c += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float* p = partial + ((size_t)s * total_pairs + pair) * (R + 2);
-            if (p[R] != -INFINITY) acc += exp2f(p[R] - M) * p[c];
+    const size_t stride = (size_t)total_pairs * (R + 4);
+    const float* base = partial + (size_t)pair * (R + 4);
+    if (threadIdx.x < 32) {
+        float m[2], l[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int s_ = threadIdx.x + 32 * i;
+            m[i] = s_ < n_splits ? base[s_ * stride + R] : -INFINITY;
+            l[i] = s_ < n_splits ? base[s_ * stride + R + 1] : 0.f;
         }
-        out[(size_t)pair * R + c] = __float2bfloat16_rn(acc * inv);
+        const float M = warp_max(fmaxf(m[0], m[1]));
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float w = (m[i] == -INFINITY) ? 0.f : exp2f(m[i] - M);
+            if (threadIdx.x + 32 * i < LAT_MERGE_MAX_SPLITS) wgt[threadIdx.x + 32 * i] = w;
+            d += w * l[i];
+        }
+        d = warp_sum(d);
+        if (threadIdx.x == 0) inv_s = d > 0.f ? 1.f / d : 0.f;
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (int c = threadIdx.x * 4; c < R; c += 128 * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int s_ = 0; s_ < n_splits; ++s_) {
+            const float4 v = *reinterpret_cast<const float4*>(base + s_ * stride + c);
+            const float w = wgt[s_];
+            acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y);
+            acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+        }
+        __nv_bfloat162 a = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), b = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+        uint2 pk;
+        pk.x = *reinterpret_cast<unsigned*>(&a);
+        pk.y = *reinterpret_cast<unsigned*>(&b);
+        *reinterpret_cast<uint2*>(out + (size_t)pair * R + c) = pk;
     }
 }
 
@@ -462,7 +489,7 @@ extern "C" int braid_latent_attn_tile_rows(int max_q_len, int heads) {
 }
 
 extern "C" long long braid_latent_attn_partial_floats(int rows, int heads, int n_splits) {
-    return (long long)n_splits * rows * heads * (R + 2);
+    return (long long)n_splits * rows * heads * (R + 4);
 }
 
 // rows: rows of the step (padding included); q [rows, heads, D], out [rows, heads, R]; rows that belong to no
@@ -476,6 +503,7 @@ extern "C" int braid_latent_attn_mma(const void* q, void* out, float* partial, c
     if (!error_flag) BRAID_REFUSE("latent_attn_mma: error_flag is required");
     if (heads <= 0 || table_cols <= 0 || num_pages <= 0) BRAID_REFUSE("latent_attn_mma: heads=%d, table columns=%d, pages=%d", heads, table_cols, num_pages);
     if (n_splits < 1 || (n_splits > 1 && !partial)) BRAID_REFUSE("latent_attn_mma: %d slices need a workspace", n_splits);
+    if (n_splits > LAT_MERGE_MAX_SPLITS) BRAID_REFUSE("latent_attn_mma: at most %d slices, not %d", LAT_MERGE_MAX_SPLITS, n_splits);
     if (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15) BRAID_REFUSE("latent_attn_mma: operands must start on 16 bytes");
     const bool few = braid_latent_attn_tile_rows(max_q_len, heads) == FEW_ROWS;
     const int tile_rows = few ? FEW_ROWS : BM;
