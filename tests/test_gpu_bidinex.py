@@ -624,3 +624,16 @@ def test_trace_replay_program_on_a_model_folder(folders, oracles, tmp_path):
     assert not (out / "2.f32").exists()
     assert rel(got[0], wa[[0, 32]]) < TOL["float32"] and rel(got[1], torch.stack([wa[33], wb[8]])) < TOL["float32"]
     assert rel(got[3], wa[39:40]) < TOL["float32"]
+
+
+def test_generate_command_line_on_a_model_folder(folders, oracles):
+    env = dict(os.environ, MODEL=folders["B"], MAX_TOKENS="6", RAW="1", DTYPE="float32", MAX_SEQ_LEN="128")
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), "7, 200, 31, 4"], env=env, capture_output=True,
+                       text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    toks, want = [7, 200, 31, 4], []
+    for _ in range(6):
+        t = P.argmax_lowest(oracles["B"].logits(toks)[-1])
+        want.append(t)
+        toks.append(t)
+    assert [int(x) for x in p.stdout.split()] == want
