@@ -4,13 +4,15 @@
 //   C[BM x BN] = A[BM x K] * B[BN x K]^T      A: a pointer per row (null: a row of zeros), k contiguous
 //                                             B: rows of a [*, K] matrix, k contiguous ([out, in] weights)
 // Both operands are k-major, so fragments come from shared memory with plain ldmatrix.  k runs in blocks of
-// 32 through two shared-memory stages filled by cp.async (16 bytes a copy: K and every row start must be
-// multiples of 8 elements; past K a copy is filled with zeros).  NB = 2 multiplies the same A tile with two
+// 32 through three shared-memory stages filled by cp.async, two blocks ahead of the one being multiplied and
+// one barrier a block (16 bytes a copy: K and every row start must be multiples of 8 elements; past K a copy
+// is filled with zeros).  NB = 2 multiplies the same A tile with two
 // B matrices at once (gate and up of a SwiGLU).  128 threads: WM x WN warps, each a (BM/WM) x (BN/WN) part.
 #pragma once
 #include "common.cuh"
 
 #define MT_BK 32
+#define MT_STAGES 3
 #define MT_LDS (MT_BK + 8)      // 80 bytes a row: eight consecutive rows fall into eight different 16-byte columns
 
 __device__ __forceinline__ void mt_cp_async16(void* smem, const void* gmem, int src_bytes) {
@@ -40,8 +42,8 @@ template <int BM, int BN, int WM, int WN, int NB>
 struct MmaTile {
     static constexpr int MI = BM / WM / 16;       // m16 tiles a warp
     static constexpr int NI = BN / WN / 8;        // n8 tiles a warp (even)
-    static constexpr int A_ELEMS = 2 * BM * MT_LDS;
-    static constexpr int B_ELEMS = 2 * BN * MT_LDS;
+    static constexpr int A_ELEMS = MT_STAGES * BM * MT_LDS;
+    static constexpr int B_ELEMS = MT_STAGES * BN * MT_LDS;
     static constexpr int SMEM_BYTES = (A_ELEMS + NB * B_ELEMS) * 2;
     static_assert(WM * WN == 4 && MI >= 1 && NI >= 2 && NI % 2 == 0, "four warps; at least 16 x 16 a warp");
 
@@ -93,16 +95,18 @@ struct MmaTile {
                 }
             mt_commit();
         };
-        load(0, 0);
+        // a group is committed for every block slot, empty where k has ended, so that the wait counts stay uniform
+#pragma unroll
+        for (int p = 0; p < MT_STAGES - 1; ++p) {
+            if (p < KT) load(p, p);
+            else mt_commit();
+        }
         for (int kt = 0; kt < KT; ++kt) {
-            const int stage = kt & 1;
-            if (kt + 1 < KT) {
-                load(kt + 1, stage ^ 1);
-                mt_wait<1>();
-            } else {
-                mt_wait<0>();
-            }
-            __syncthreads();
+            const int stage = kt % MT_STAGES;
+            mt_wait<MT_STAGES - 2>();          // block kt has arrived (this thread's copies)
+            __syncthreads();                   // ... everybody's; and everybody is done with block kt - 1,
+            if (kt + MT_STAGES - 1 < KT) load(kt + MT_STAGES - 1, (kt + MT_STAGES - 1) % MT_STAGES);   // whose stage is filled next
+            else mt_commit();
 #pragma unroll
             for (int ks = 0; ks < MT_BK / 16; ++ks) {
                 unsigned af[MI][4];
@@ -123,7 +127,7 @@ struct MmaTile {
                         }
                     }
             }
-            __syncthreads();
         }
+        mt_wait<0>();
     }
 };
