@@ -17,7 +17,7 @@ from typing import List, Optional, Sequence, Union
 from .cache import PAGE_SIZE
 from .config import preset, read_config_json
 from .engine.engine import Engine
-from .models import architecture_for
+from .models import architecture_for, complete_config
 from .weights import tensor_specs_of
 from .engine.generate import Completion, GenerationLoop, GenerationStats
 from .sampling import Sampler, SamplingParams
@@ -108,7 +108,8 @@ def load(model: str, dtype: str = "bfloat16", max_seq_len: Optional[int] = None,
     else:
         if not os.path.isdir(model):
             raise FileNotFoundError(f"MODEL={model!r} is not a folder (use a model folder or random:<preset>)")
-        cfg_dict = read_config_json(model)
+        from .weights.safetensors_io import tensor_shapes
+        cfg_dict = complete_config(read_config_json(model), tensor_shapes(model))
         source = model
     arch = architecture_for(cfg_dict)
     spec = arch.build_spec(arch.config_from_dict(cfg_dict))

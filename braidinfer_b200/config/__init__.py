@@ -2,6 +2,7 @@
 from .errors import ConfigError, UnknownArchitectureError
 from .mistral import MistralConfig
 from .bidinex import BidinexConfig
+from .loduzen import LoduzenConfig
 from .presets import PRESETS, preset
 
 

@@ -16,6 +16,13 @@ import torch
 from . import build
 
 F32, BF16 = 0, 1
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}      # the gate's activation in gated feed-forwards (common.cuh BRAID_ACT_*)
+
+
+def activation_code(name: str) -> int:
+    if name not in ACTIVATIONS:
+        raise KernelError(f"unknown activation {name!r}; the kernels have {sorted(ACTIVATIONS)}")
+    return ACTIVATIONS[name]
 
 
 class KernelError(RuntimeError):
@@ -127,6 +134,12 @@ class Kernels:
         L.braid_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
         L.braid_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
         L.braid_silu_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        L.braid_act_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        L.braid_head_norm_rope_kv.argtypes = [c_void_p, c_longlong, c_int] + [c_void_p] * 7 + [c_int] * 10 + \
+                                             [c_float, c_float, c_void_p, c_void_p]
+        L.braid_act_mul_gather.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
+                                           c_int, c_int, c_int, c_int, c_void_p]
+        L.braid_rmsnorm_add.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
         L.braid_residual_add.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
         L.braid_rope_kv_write.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -136,7 +149,7 @@ class Kernels:
         L.braid_gather_i32.restype = c_int
         L.braid_attn_simple.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                        c_float, c_void_p, c_void_p]
+                                        c_float, c_int, c_float, c_float, c_void_p, c_void_p]
         L.braid_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                       c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
         scale = [c_void_p, c_int, c_longlong, c_float, c_float]        # RowScale.args()
@@ -165,7 +178,8 @@ class Kernels:
         L.braid_concat2.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         for name in ("braid_dyt", "braid_softcap", "braid_concat2"):
             getattr(L, name).restype = c_int
-        for name in ("braid_embed", "braid_rmsnorm", "braid_silu_mul", "braid_residual_add",
+        for name in ("braid_embed", "braid_rmsnorm", "braid_silu_mul", "braid_act_mul", "braid_head_norm_rope_kv",
+                     "braid_act_mul_gather", "braid_rmsnorm_add", "braid_residual_add",
                      "braid_rope_kv_write", "braid_cast", "braid_attn_simple", "braid_gemm_simt",
                      "braid_gemm_tc", "braid_gemm_tc2", "braid_argmax", "braid_sample", "braid_streamk_reduce",
                      "braid_streamk_reduce_norm", "braid_streamk_reduce_rope_kv", "braid_streamk_reduce_prep",
@@ -231,10 +245,60 @@ class Kernels:
                                            self._stream()), "rmsnorm")
 
     def silu_mul(self, gu: torch.Tensor, out: torch.Tensor) -> None:
+        self.act_mul(gu, out, "silu")
+
+    def act_mul(self, gu: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+        """out = act(gu[:, :I]) * gu[:, I:], I = out's width."""
         rows, inter = out.shape
         self.launches += 1
-        self._check(self.lib.braid_silu_mul(gu.data_ptr(), out.data_ptr(), dtype_code(out.dtype), rows, inter,
-                                            self._stream()), "silu_mul")
+        self._check(self.lib.braid_act_mul(gu.data_ptr(), out.data_ptr(), dtype_code(out.dtype), rows, inter,
+                                           activation_code(activation), self._stream()), "act_mul")
+
+    def head_norm_rope_kv(self, qk: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                          inv_freq: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
+                          page_table: Optional[torch.Tensor], cache: Optional[torch.Tensor], nqh: int, nkh: int, hd: int,
+                          rope_dim: int, adjacent: bool, value_is_key: bool, page_size: int, eps: float,
+                          amp: float = 1.0) -> None:
+        """Rows of stacked heads [rows, >= (nqh + nkh (+ nkh)) * hd]: every query and key head is RMS-normed over
+        the head with q_w / k_w ([hd], shared by the heads; None: no norm), rotated (sine and cosine times `amp`)
+        and written back; keys also go into the cache's key plane, and the value plane takes the value heads, or,
+        with `value_is_key`, the key heads as they came in (before norm and rotation)."""
+        for w in (q_w, k_w):
+            if w is not None and (w.dtype != qk.dtype or w.numel() != hd):
+                raise KernelError(f"head_norm_rope_kv: a norm weight must hold {hd} numbers of the rows' element type")
+        if cache is not None and cache.dtype != qk.dtype:
+            raise KernelError("head_norm_rope_kv: rows and cache must have one element type")
+        if qk.stride(1) != 1 or qk.shape[1] < (nqh + (nkh if value_is_key else 2 * nkh)) * hd:
+            raise KernelError("head_norm_rope_kv: the rows do not hold the heads")
+        cols = page_table.shape[1] if page_table is not None else 0
+        self.launches += 1
+        self._check(self.lib.braid_head_norm_rope_kv(
+            qk.data_ptr(), qk.stride(0), dtype_code(qk.dtype), _ptr(q_w), _ptr(k_w), inv_freq.data_ptr(),
+            positions.data_ptr(), token_seq.data_ptr(), _ptr(page_table), _ptr(cache), qk.shape[0], nqh, nkh, hd,
+            rope_dim, int(adjacent), int(value_is_key), page_size, cols, cache.shape[0] if cache is not None else 0,
+            float(eps), float(amp), self._error_flag.data_ptr(), self._stream()), "head_norm_rope_kv")
+
+    def act_mul_gather(self, gate: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int, out: torch.Tensor,
+                       activation: str) -> None:
+        """out[r, j] = act(gate[r, j]) * table[ids[r], col0 + j]."""
+        rows, dim = out.shape
+        if not (gate.dtype == table.dtype == out.dtype) or not out.is_contiguous() or gate.stride(1) != 1 \
+                or table.stride(1) != 1 or col0 + dim > table.shape[1] or gate.shape[1] < dim:
+            raise KernelError("act_mul_gather: gate, table and out of one element type; the table must hold the columns")
+        self.launches += 1
+        self._check(self.lib.braid_act_mul_gather(gate.data_ptr(), gate.stride(0), table.data_ptr(), table.stride(0),
+                                                  ids.data_ptr(), table.shape[0], int(col0), out.data_ptr(),
+                                                  dtype_code(out.dtype), rows, dim, activation_code(activation),
+                                                  self._stream()), "act_mul_gather")
+
+    def rmsnorm_add(self, h: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float) -> None:
+        """h += y / sqrt(mean(y^2) + eps) * w, row by row; h and y float32 [rows, width], contiguous."""
+        if h.dtype != torch.float32 or y.dtype != torch.float32 or h.shape != y.shape or not h.is_contiguous() \
+                or not y.is_contiguous() or w.numel() != h.shape[1]:
+            raise KernelError("rmsnorm_add: h and y are contiguous float32 of one shape, w one number a column")
+        self.launches += 1
+        self._check(self.lib.braid_rmsnorm_add(h.data_ptr(), y.data_ptr(), w.data_ptr(), dtype_code(w.dtype), h.shape[0],
+                                               h.shape[1], float(eps), self._stream()), "rmsnorm_add")
 
     def residual_add(self, h: torch.Tensor, delta: torch.Tensor) -> None:
         self.launches += 1
@@ -265,14 +329,18 @@ class Kernels:
 
     def attn_simple(self, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
                     positions: torch.Tensor, token_seq: torch.Tensor, nqh: int, nkh: int, hd: int,
-                    page_size: int, window: Optional[int], scale: float) -> None:
-        """q: [rows, >= nqh*hd] (a view of the qkv rows is fine), out: [rows, nqh*hd]."""
+                    page_size: int, window: Optional[int], scale: float, sink: Optional[float] = None,
+                    out_scale: float = 1.0) -> None:
+        """q: [rows, >= nqh*hd] (a view of the qkv rows is fine), out: [rows, nqh*hd].  `sink`: the score of an
+        attention sink, one more term of the softmax's denominator that has no value (None: no sink);
+        `out_scale`: a constant factor on the result."""
         rows = out.shape[0]
         self.launches += 1
         self._check(self.lib.braid_attn_simple(
             q.data_ptr(), out.data_ptr(), dtype_code(out.dtype), cache.data_ptr(), page_table.data_ptr(),
             positions.data_ptr(), token_seq.data_ptr(), q.stride(0), out.stride(0), rows, nqh, nkh, hd,
             page_size, page_table.shape[1], cache.shape[0], int(window or 0), float(scale),
+            int(sink is not None), float(sink or 0.0), float(out_scale),
             self._error_flag.data_ptr() + 16, self._stream()),
             "attn_simple")
 
@@ -289,7 +357,7 @@ class Kernels:
             lib = ctypes.CDLL(str(build.attention_library(head_dim, verbose=self._verbose)))
             lib.braid_last_error.restype = c_char_p
             lib.braid_attn_mma.restype = c_int
-            lib.braid_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 13 + [c_float, c_void_p, c_void_p]
+            lib.braid_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 13 + [c_float, c_int, c_float, c_float, c_void_p, c_void_p]
             lib.braid_attn_mma_partial_floats.restype = c_longlong
             lib.braid_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
             lib.braid_attn_tc_supported.restype = c_int
@@ -338,9 +406,11 @@ class Kernels:
     def attn_mma(self, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
                  q_start: torch.Tensor, q_len: torch.Tensor, kv_before: torch.Tensor, token_seq: torch.Tensor,
                  n_seqs: int, max_q_len: int, nqh: int, nkh: int, hd: int, window: Optional[int], scale: float,
-                 n_splits: int = 1, few_tokens: bool = False) -> None:
+                 n_splits: int = 1, few_tokens: bool = False, sink: Optional[float] = None,
+                 out_scale: float = 1.0) -> None:
         """bfloat16 attention over the cache on the tensor cores; `n_splits` > 1 slices the
-        context (for steps of few tokens) and merges the slices in a second kernel."""
+        context (for steps of few tokens) and merges the slices in a second kernel.  `sink` and
+        `out_scale` as in `attn_simple` (the sink is counted once, where the slices merge)."""
         lib = self.attn_mma_library(hd)
         self._check_pages(cache)
         rows = out.shape[0]
@@ -357,7 +427,8 @@ class Kernels:
                                 q_start.data_ptr(), q_len.data_ptr(), kv_before.data_ptr(), token_seq.data_ptr(),
                                 q.stride(0), out.stride(0), rows, n_seqs, max_q_len, nqh, nkh, hd,
                                 page_table.shape[1], cache.shape[0], int(window or 0), n_splits,
-                                1 if few_tokens else 0, float(scale), self._error_flag.data_ptr() + 16, self._stream())
+                                1 if few_tokens else 0, float(scale), int(sink is not None), float(sink or 0.0),
+                                float(out_scale), self._error_flag.data_ptr() + 16, self._stream())
         if rc != 0:
             raise KernelError(f"attn_mma: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
 
@@ -407,6 +478,15 @@ class Kernels:
                 lib.braid_attn_latent_simple.argtypes = [c_void_p, c_void_p, c_int] + [c_void_p] * 4 + \
                                                         [c_longlong, c_longlong] + [c_int] * 8 + [c_float, c_void_p, c_void_p]
                 names = ("braid_latent_prep", "braid_gemm_heads", "braid_attn_latent_simple")
+            elif name == "scan":
+                lib.braid_causal_conv.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
+                                                  c_void_p, c_longlong, c_longlong] + [c_void_p] * 4 + [c_int] * 5 + [c_void_p]
+                lib.braid_linear_scan.argtypes = [c_void_p, c_longlong] * 4 + [c_void_p] * 3 + [c_void_p, c_longlong] + \
+                                                 [c_void_p, c_longlong, c_longlong] + [c_void_p] * 3 + [c_int] * 7 + \
+                                                 [c_float, c_float, c_void_p]
+                lib.braid_gated_norm.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong,
+                                                 c_void_p] + [c_int] * 5 + [c_float, c_float, c_void_p]
+                names = ("braid_causal_conv", "braid_linear_scan", "braid_gated_norm")
             elif name == "moe":
                 lib.braid_moe_route.argtypes = [c_void_p] * 3 + [c_int] * 5 + [c_float, c_void_p]
                 lib.braid_moe_plan.argtypes = [c_void_p] * 6 + [c_int] * 5 + [c_void_p]
@@ -658,6 +738,78 @@ class Kernels:
                                                    wgt.data_ptr(), rows, width, wgt.shape[1], y.stride(0), self._stream()),
                         "moe_combine")
 
+    # ------------------------------------------------------------------ mixers with a recurrent state
+    @staticmethod
+    def _state_args(state: torch.Tensor, offset: int):
+        if state.dtype != torch.uint8 or state.dim() != 2 or state.stride(1) != 1:
+            raise KernelError("a state area is a uint8 tensor [slots, bytes]")
+        return state.data_ptr(), state.stride(0), int(offset)
+
+    def causal_conv(self, x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], state: torch.Tensor,
+                    state_offset: int, ctx, silu: bool = True) -> None:
+        """y[t, c] = act(b[c] + sum_j w[c, j] x[t - (taps - 1 - j), c]) along each sequence of the step (x, y
+        [rows, channels], views are fine; w [channels, taps]); inputs before the step come from the state
+        (float32 [taps - 1, channels] at `state_offset` bytes of each slot), which is then moved on."""
+        lib = self.part_library("scan")
+        rows, channels = y.shape
+        taps = w.shape[1]
+        if not (x.dtype == y.dtype == w.dtype) or (b is not None and b.dtype != x.dtype) or x.stride(1) != 1 \
+                or y.stride(1) != 1 or not w.is_contiguous() or w.shape[0] != channels or x.shape[1] != channels:
+            raise KernelError("causal_conv: x, y, w, b of one element type; w contiguous [channels, taps]")
+        self.launches += 2 if taps > 1 else 1
+        self._check_lib(lib, lib.braid_causal_conv(
+            x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), w.data_ptr(), _ptr(b), dtype_code(x.dtype),
+            *self._state_args(state, state_offset), ctx.token_seq.data_ptr(), ctx.q_start.data_ptr(),
+            ctx.q_len.data_ptr(), ctx.slot_ids.data_ptr(), rows, ctx.n_seqs, channels, taps, int(silu), self._stream()),
+            "causal_conv")
+
+    def linear_scan(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor, gate_bias: torch.Tensor,
+                    out: torch.Tensor, state: torch.Tensor, state_offset: int, ctx, heads: int, groups: int, dk: int,
+                    dv: int, mode: str, q_scale: float = 1.0, inv_tau: float = 1.0, a_log: Optional[torch.Tensor] = None,
+                    skip: Optional[torch.Tensor] = None) -> None:
+        """The recurrence S <- diag(a) S + (kappa k) v^T, o = S^T (q_scale q) + skip v, token by token along each
+        sequence of the step, S float32 [heads, dk, dv] at `state_offset` bytes of each slot.  mode "channel":
+        a = sigmoid(gate + gate_bias)^inv_tau per key channel (gate float32 [rows, heads * dk]); mode "head":
+        dt = softplus(gate + gate_bias), a = exp(-exp(a_log) dt), kappa = dt (gate [rows, heads] in the run's
+        type).  q, k [rows, groups * dk], v [rows, heads * dv] (views are fine); out float32 [rows, heads * dv]."""
+        lib = self.part_library("scan")
+        if not (q.dtype == k.dtype == v.dtype == gate_bias.dtype) or out.dtype != torch.float32 \
+                or any(t.stride(1) != 1 for t in (q, k, v, gate, out)):
+            raise KernelError("linear_scan: q, k, v and the gate's bias of one element type, out float32, rows contiguous")
+        if mode == "channel":
+            if gate.dtype != torch.float32 or gate.shape[1] != heads * dk or gate_bias.numel() != heads * dk:
+                raise KernelError("linear_scan: a decay per channel takes a float32 gate [rows, heads * dk]")
+        elif mode == "head":
+            if gate.dtype != q.dtype or gate.shape[1] != heads or gate_bias.numel() != heads or a_log is None \
+                    or a_log.dtype != q.dtype or (skip is not None and skip.dtype != q.dtype):
+                raise KernelError("linear_scan: a decay per head takes a gate [rows, heads], its bias, A_log and a skip "
+                                  "of the rows' element type")
+        else:
+            raise KernelError(f"linear_scan: unknown decay mode {mode!r}")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_linear_scan(
+            q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), gate.data_ptr(), gate.stride(0),
+            gate_bias.data_ptr(), _ptr(a_log), _ptr(skip), out.data_ptr(), out.stride(0),
+            *self._state_args(state, state_offset), ctx.q_start.data_ptr(), ctx.q_len.data_ptr(), ctx.slot_ids.data_ptr(),
+            dtype_code(q.dtype), 0 if mode == "channel" else 1, ctx.n_seqs, heads, groups, dk, dv, float(q_scale),
+            float(inv_tau), self._stream()), "linear_scan")
+
+    def gated_norm(self, y: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, out: torch.Tensor, token_seq: torch.Tensor,
+                   group: int, gate_first: bool, eps: float, out_scale: float = 1.0) -> None:
+        """Groups of `group` columns of y (float32 [rows, width]), each by its own root mean square: norm then
+        silu(gate), or (gate_first) silu(gate) then norm; times w (one weight a group's column, or one a column of
+        the row) and out_scale."""
+        lib = self.part_library("scan")
+        rows, width = y.shape
+        if y.dtype != torch.float32 or not y.is_contiguous() or not (gate.dtype == w.dtype == out.dtype) \
+                or gate.stride(1) != 1 or out.stride(1) != 1 or w.numel() not in (group, width) or tuple(out.shape) != (rows, width):
+            raise KernelError("gated_norm: y contiguous float32; gate, w, out of one element type; w of a group's or a row's length")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_gated_norm(
+            y.data_ptr(), gate.data_ptr(), gate.stride(0), w.data_ptr(), w.numel(), out.data_ptr(), out.stride(0),
+            token_seq.data_ptr(), dtype_code(out.dtype), rows, width, group, int(gate_first), float(eps), float(out_scale),
+            self._stream()), "gated_norm")
+
     # ------------------------------------------------------------------ matrix products
     def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> None:
         n, k = x.shape
@@ -688,7 +840,7 @@ class Kernels:
 
     def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
                 swiglu: bool = False, block_n: int = 0, stream_k: bool = False,
-                in_scale: Optional[RowScale] = None) -> None:
+                in_scale: Optional[RowScale] = None, activation: str = "silu") -> None:
         """bfloat16 x [n, k] times w [m, k]^T on the tensor cores.  With `swiglu`, w holds
         gate and up rows interleaved in blocks of 16 (`interleave_gate_up`) and out is [n, I].  `stream_k` spreads the weight stream
         evenly over all SMs whatever the shape (for up to a few hundred tokens) and adds a reduce kernel.
@@ -697,13 +849,13 @@ class Kernels:
         `in_scale`: a row scale that x still wants; the store and SwiGLU epilogues apply it to their results."""
         n, k = x.shape
         if not stream_k and block_n == 0 and token_tile(n) == PAIR_TOKEN_TILE and in_scale is None:
-            return self.gemm_tc_pair(x, w, out, residual=residual, swiglu=swiglu)
+            return self.gemm_tc_pair(x, w, out, residual=residual, swiglu=swiglu, activation=activation)
         w_rows = w.shape[0]
         m = out.shape[1] if swiglu else w_rows
         if swiglu and w_rows != 2 * (-(-m // 16) * 16):
             raise KernelError(f"the SwiGLU epilogue wants {2 * (-(-m // 16) * 16)} interleaved weight rows for "
                               f"{m} outputs, got {w_rows} (see interleave_gate_up)")
-        mode = 2 if swiglu else (1 if residual is not None else 0)
+        mode = (2 | activation_code(activation) << 4) if swiglu else (1 if residual is not None else 0)
         block_n = block_n or token_tile(n)
         ws = None
         if stream_k:
@@ -726,7 +878,8 @@ class Kernels:
         return torch.empty(-(-n // 4) * 4, dtype=torch.float32, device=device)
 
     def gemm_tc_pair(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
-                     residual: Optional[torch.Tensor] = None, swiglu: bool = False, direct_out: bool = False) -> None:
+                     residual: Optional[torch.Tensor] = None, swiglu: bool = False, direct_out: bool = False,
+                     activation: str = "silu") -> None:
         """As `gemm_tc` with whole tiles, on pairs of SMs: tiles of 256 weight rows x 256 tokens, each CTA of
         a pair loading half of both operands (tcgen05.mma.cta_group::2).  For prompts.  The output leaves
         through TMA stores (a TMA reduce-add for a residual summed in place) where it can be addressed so;
@@ -737,7 +890,7 @@ class Kernels:
         if swiglu and w_rows != 2 * (-(-m // 16) * 16):
             raise KernelError(f"the SwiGLU epilogue wants {2 * (-(-m // 16) * 16)} interleaved weight rows for "
                               f"{m} outputs, got {w_rows} (see interleave_gate_up)")
-        mode = 2 if swiglu else (1 if residual is not None else 0)
+        mode = (2 | activation_code(activation) << 4) if swiglu else (1 if residual is not None else 0)
         self.launches += 1
         self._check(self.lib.braid_gemm_tc2(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual),
                                             dtype_code(out.dtype), mode, n, m, k, x.stride(0), w.stride(0),
@@ -772,9 +925,9 @@ class Kernels:
         self.pending_partial = None
 
     def streamk_reduce(self, p: "PartialProduct", out: torch.Tensor, residual: Optional[torch.Tensor] = None,
-                       swiglu: bool = False) -> None:
+                       swiglu: bool = False, activation: str = "silu") -> None:
         m = out.shape[1] if swiglu else p.w_rows
-        mode = 2 if swiglu else (1 if residual is not None else 0)
+        mode = (2 | activation_code(activation) << 4) if swiglu else (1 if residual is not None else 0)
         self._close_partial(p)
         self.launches += 1
         self._check(self.lib.braid_streamk_reduce(p.workspace.data_ptr(), p.plan, p.n_rows, out.data_ptr(), _ptr(residual),

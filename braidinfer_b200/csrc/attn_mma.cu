@@ -40,6 +40,9 @@ struct AttnMmaArgs {
     float scale_log2;            // softmax scale * log2(e)
     int num_pages;               // pages of the cache: a table entry outside [0, num_pages) is never followed
     int* error_flag;             // raised when a tile of visible keys has no page or one outside the cache
+    int has_sink;                // the denominator counts one more term 2^sink_log2 that has no value (an attention sink)
+    float sink_log2;             // the sink's score * log2(e)
+    float out_scale;             // a constant factor on the result
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -278,9 +281,16 @@ attn_mma_kernel(AttnMmaArgs a) {
         const int tl = row / hpc, hl = row - tl * hpc;
         const size_t grow = (size_t)(q_start + tok0 + tl);
         const int head = head0 + hl;
-        const float l = half ? l_b : l_a, m = half ? m_b : m_a;
+        float l = half ? l_b : l_a;
+        const float m = half ? m_b : m_a;
         if (a.n_splits == 1) {
-            const float inv = 1.f / l;
+            float corr = 1.f;
+            if (a.has_sink) {                            // the sink joins as one more score, with no value
+                const float mn = fmaxf(m, a.sink_log2);
+                corr = exp2f(m - mn);                    // exp2(-inf) = 0
+                l = l * corr + exp2f(a.sink_log2 - mn);
+            }
+            const float inv = corr * a.out_scale / l;
             __nv_bfloat16* dst = a.out + grow * a.out_row_stride + (size_t)head * HD + (lane & 3) * 2;
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i)
@@ -301,7 +311,8 @@ attn_mma_kernel(AttnMmaArgs a) {
 #define COMBINE_MAX_SPLITS 64
 template <int HD>
 __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
-                                    const int* __restrict__ token_seq, int out_row_stride, int nqh, int n_splits) {
+                                    const int* __restrict__ token_seq, int out_row_stride, int nqh, int n_splits,
+                                    int has_sink, float sink_log2, float out_scale) {
     pdl_trigger();
     // the step's tables are on the device before the step's first kernel: read before the wait
     const int row = blockIdx.x, head = blockIdx.y;
@@ -337,7 +348,13 @@ __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bflo
             }
             M = Mn;
         }
-        out[(size_t)row * out_row_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+        if (has_sink) {                                    // once for the whole row, not once a slice
+            const float Mn = fmaxf(M, sink_log2);
+            const float c = exp2f(M - Mn);
+            L = L * c + exp2f(sink_log2 - Mn);
+            acc *= c;
+        }
+        out[(size_t)row * out_row_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc * out_scale / L);
     }
 }
 
@@ -388,7 +405,7 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
                               const int* q_start, const int* q_len, const int* kv_before, const int* token_seq,
                               int q_row_stride, int out_row_stride, int rows, int n_seqs, int max_q_len,
                               int nqh, int nkh, int hd, int table_cols, int num_pages, int window, int n_splits, int kind,
-                              float scale, int* error_flag, void* stream) {
+                              float scale, int has_sink, float sink_score, float out_scale, int* error_flag, void* stream) {
     if (rows <= 0 || n_seqs <= 0) return BRAID_OK;
     if (!error_flag) BRAID_REFUSE("attn_mma: error_flag is required");
     if (num_pages <= 0 || table_cols <= 0) BRAID_REFUSE("attn_mma: the cache has no pages (pages=%d, table columns=%d)", num_pages, table_cols);
@@ -400,7 +417,7 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
     if (n_splits > 1 && !partial) BRAID_REFUSE("attn_mma: n_splits > 1 needs the partial buffer");
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (float*)partial, (const __nv_bfloat16*)cache, page_table,
                   q_start, q_len, kv_before, q_row_stride, out_row_stride, nqh, nkh, table_cols, window, n_splits,
-                  scale * 1.4426950408889634f, num_pages, error_flag};
+                  scale * 1.4426950408889634f, num_pages, error_flag, has_sink, sink_score * 1.4426950408889634f, out_scale};
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
     if (kind == 0) rc = launch_attn<4, 64, 2>(a, n_seqs, max_q_len, s);
@@ -408,7 +425,7 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
     if (rc) return rc;
     if (n_splits > 1) {
         dim3 grid(rows, nqh);
-        braid_launch(attn_combine_kernel<BRAID_HD>, grid, dim3(BRAID_HD >= 128 ? 128 : 32), 0, s, (const float*)partial, (__nv_bfloat16*)out, token_seq, out_row_stride, nqh, n_splits);
+        braid_launch(attn_combine_kernel<BRAID_HD>, grid, dim3(BRAID_HD >= 128 ? 128 : 32), 0, s, (const float*)partial, (__nv_bfloat16*)out, token_seq, out_row_stride, nqh, n_splits, has_sink, sink_score * 1.4426950408889634f, out_scale);
         BRAID_LAUNCH_CHECK();
     }
     return BRAID_OK;
@@ -455,5 +472,5 @@ extern "C" int braid_attn_mma_noalloc(const void* q, void* out, const void* cach
     }
     return braid_attn_mma(q, out, n_splits > 1 ? g_noalloc_ptr[dev] : nullptr, cache, page_table, q_start, q_len,
                           kv_before, token_seq, q_row_stride, out_row_stride, rows, n_seqs, max_q_len, nqh, nkh, hd,
-                          table_cols, num_pages, window, n_splits, kind, scale, error_flag, stream);
+                          table_cols, num_pages, window, n_splits, kind, scale, 0, 0.f, 1.f, error_flag, stream);
 }

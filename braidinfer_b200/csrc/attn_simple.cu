@@ -10,6 +10,9 @@
 // denominator d and accumulator acc; out = acc / d.  Key j is visible to the query at
 // position p iff j <= p and, with a window w > 0, p - j < w (the window is this
 // library's own; the reference has none).  Scores, softmax and accumulation are float32.
+// With has_sink, the denominator also counts one more term exp(sink_score) that has no value
+// (an attention sink: p_j = exp(s_j) / (exp(sink_score) + sum_i exp(s_i))).  out_scale is a
+// constant factor on the result.
 #include "common.cuh"
 
 struct AttnSimpleArgs {
@@ -22,6 +25,8 @@ struct AttnSimpleArgs {
     int q_row_stride, out_row_stride;
     int rows, nqh, nkh, hd, page_size, table_cols, num_pages, window;
     float scale;
+    int has_sink;
+    float sink_score, out_scale;
     int* error_flag;          // raised when a visible position has no page, or one outside the cache
 };
 
@@ -99,7 +104,13 @@ attn_simple_kernel(AttnSimpleArgs a) {
         }
         __syncwarp();
     }
-    const float inv = 1.f / l;
+    float corr_end = 1.f;
+    if (a.has_sink) {                                // the sink joins as one more score, with no value
+        const float m_new = fmaxf(m, a.sink_score);
+        corr_end = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        l = l * corr_end + expf(a.sink_score - m_new);
+    }
+    const float inv = corr_end * a.out_scale / l;
 #pragma unroll
     for (int i = 0; i < ATTN_SIMPLE_MAX_HD / 32; ++i) {
         const int d = lane + 32 * i;
@@ -111,6 +122,7 @@ extern "C" int braid_attn_simple(const void* q, void* out, int dtype, const void
                                  const int* page_table, const int* positions, const int* token_seq,
                                  int q_row_stride, int out_row_stride, int rows, int nqh, int nkh, int hd,
                                  int page_size, int table_cols, int num_pages, int window, float scale,
+                                 int has_sink, float sink_score, float out_scale,
                                  int* error_flag, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (!error_flag) BRAID_REFUSE("attn_simple: error_flag is required");
@@ -118,7 +130,7 @@ extern "C" int braid_attn_simple(const void* q, void* out, int dtype, const void
     if (nqh <= 0 || nkh <= 0 || nqh % nkh != 0) BRAID_REFUSE("attn_simple: %d query heads do not divide into %d kv heads", nqh, nkh);
     if (hd <= 0 || hd > ATTN_SIMPLE_MAX_HD) BRAID_REFUSE("attn_simple: head_dim=%d outside (0, %d]", hd, ATTN_SIMPLE_MAX_HD);
     AttnSimpleArgs a{q, out, cache, page_table, positions, token_seq, q_row_stride, out_row_stride,
-                     rows, nqh, nkh, hd, page_size, table_cols, num_pages, window, scale, error_flag};
+                     rows, nqh, nkh, hd, page_size, table_cols, num_pages, window, scale, has_sink, sink_score, out_scale, error_flag};
     const long long items = (long long)rows * nqh;
     const long long blocks = (items + ATTN_SIMPLE_WARPS - 1) / ATTN_SIMPLE_WARPS;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("attn_simple: %lld (token, head) pairs exceed one launch", items);

@@ -31,7 +31,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "pointwise.cu", "attn_simple.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_tc2.cu",
                 "fused_reduce.cu", "sampling.cu"]
 # Kernels that only some models use: each a library of its own, compiled when a model that needs it is built.
-PART_SOURCES = {"latent": ["errors.cu", "latent.cu"], "moe": ["errors.cu", "moe.cu"]}
+PART_SOURCES = {"latent": ["errors.cu", "latent.cu"], "moe": ["errors.cu", "moe.cu"], "scan": ["errors.cu", "scan.cu"]}
 HEADERS = ["common.cuh", "rowscale.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h", "page.h", "trace.cuh",
            "mma_tile.cuh"]
 
@@ -168,7 +168,8 @@ def core_library(verbose: bool = True) -> Path:
 
 
 def part_library(name: str, verbose: bool = True) -> Path:
-    """The kernels of one kind of part ("latent": latent attention, "moe": mixture of experts)."""
+    """The kernels of one kind of part ("latent": latent attention, "moe": mixture of experts, "scan": mixers
+    with a recurrent state)."""
     if name not in PART_SOURCES:
         raise BuildError(f"no kernel library named {name!r}; known: {sorted(PART_SOURCES)}")
     return build_library(f"braidinfer_{name}", PART_SOURCES[name], verbose=verbose)

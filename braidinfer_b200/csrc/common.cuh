@@ -77,6 +77,27 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// Activations of the gated feed-forwards, out = act(gate) * up.  An entry point that takes an epilogue
+// `mode` takes the activation's code in bits 4..7 of it (0: silu).
+#define BRAID_ACT_SILU 0
+#define BRAID_ACT_GELU_TANH 1
+#define BRAID_ACT_COUNT 2
+// gelu in its tanh form, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) = z * sigmoid(2 u), u the tanh's argument
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+    const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    return 0.5f * z * (1.f + tanhf(u));
+}
+__device__ __forceinline__ float silu_f32(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float glu_act(float g, int act) {
+    return act == BRAID_ACT_GELU_TANH ? gelu_tanh_f32(g) : silu_f32(g);
+}
+// The same with the fast exponential and division: a few ulp, far inside the bfloat16 rounding of the
+// result, and no slow path for the infinities that the exponential reaches (g / inf = 0 is the right limit).
+__device__ __forceinline__ float glu_act_fast(float g, int act) {
+    const float e = act == BRAID_ACT_GELU_TANH ? -1.5957691216057308f * (g + 0.044715f * g * g * g) : -g;
+    return __fdividef(g, 1.f + __expf(e));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

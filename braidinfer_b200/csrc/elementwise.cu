@@ -168,10 +168,10 @@ extern "C" int braid_rmsnorm(const float* x, const void* w, int w_dtype, void* o
     BRAID_LAUNCH_CHECK();
 }
 
-// ------------------------------------------------------------------ silu(gate) * up
-// gu is [rows, 2*inter]: gate in columns [0, inter), up in [inter, 2*inter).
+// ------------------------------------------------------------------ act(gate) * up
+// gu is [rows, 2*inter]: gate in columns [0, inter), up in [inter, 2*inter).  act: BRAID_ACT_*.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inter, int act) {
     pdl_trigger();
     pdl_wait();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -180,19 +180,25 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
     const int c = (int)(i - r * inter);
     const float g = to_f32(gu[r * 2 * inter + c]);
     const float u = to_f32(gu[r * 2 * inter + inter + c]);
-    out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    out[i] = from_f32<T>(glu_act(g, act) * u);
 }
 
+extern "C" int braid_act_mul(const void* gu, void* out, int dtype, int rows, int inter, int act, void* stream);
 extern "C" int braid_silu_mul(const void* gu, void* out, int dtype, int rows, int inter, void* stream) {
+    return braid_act_mul(gu, out, dtype, rows, inter, BRAID_ACT_SILU, stream);
+}
+
+extern "C" int braid_act_mul(const void* gu, void* out, int dtype, int rows, int inter, int act, void* stream) {
     if (rows <= 0) return BRAID_OK;
+    if (act < 0 || act >= BRAID_ACT_COUNT) BRAID_REFUSE("act_mul: unknown activation %d", act);
     if (inter <= 0) BRAID_REFUSE("silu_mul: inter=%d must be positive", inter);
     const long long total = (long long)rows * inter;
     const int threads = 256;
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("silu_mul: %lld elements exceed one launch", total);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == BRAID_F32) braid_launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, (float*)out, total, inter);
-    else if (dtype == BRAID_BF16) braid_launch(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter);
+    if (dtype == BRAID_F32) braid_launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, (float*)out, total, inter, act);
+    else if (dtype == BRAID_BF16) braid_launch(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter, act);
     else BRAID_REFUSE("silu_mul: unknown dtype code %d", dtype);
     BRAID_LAUNCH_CHECK();
 }
@@ -395,6 +401,158 @@ extern "C" int braid_rope_kv_write(void* qkv, int dtype, const float* inv_freq, 
     if (dtype == BRAID_F32) braid_launch(rope_kv_kernel<float>, dim3(grid), dim3(threads), 0, s, a);
     else if (dtype == BRAID_BF16) braid_launch(rope_kv_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, s, a);
     else BRAID_REFUSE("rope_kv_write: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ head norm + rotary + cache write
+// For mixers that norm every query and key head before the rotation (RMS norm over the head with a
+// weight of head_dim numbers shared by all heads) and, optionally, keep the key AS PROJECTED (before
+// norm and rotation) as the value.  qk: [rows, row_stride], query heads then key heads (then value
+// heads unless value_is_key).  One warp per (row, head): queries are normed and rotated in place;
+// keys are normed, rotated, written in place and to the cache's key plane; the value plane takes the
+// value head, or the key head as it came in.  The rotation turns the first rope_dim numbers of a head,
+// pair (2p, 2p+1) if adjacent else (p, p + rope_dim/2), by angle pos * inv_freq[p]; sine and cosine
+// are multiplied by `amp` (1 for a plain rotation).  Norm, angles and rotation are float32.
+struct HeadNormRopeArgs {
+    void* qk;
+    long long row_stride;
+    const void* q_w;             // [hd] or null (no norm on queries)
+    const void* k_w;             // [hd] or null
+    const float* inv_freq;       // [rope_dim / 2]
+    const int* positions;
+    const int* token_seq;
+    const int* page_table;
+    void* cache;                 // [page][2][nkh][page_size][hd] or null
+    int rows, nqh, nkh, hd, rope_dim, adjacent, value_is_key;
+    int page_size, table_cols, num_pages;
+    float eps, amp;
+    int* error_flag;
+};
+
+#define HEAD_NORM_MAX_HD 512
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_rope_kv_kernel(HeadNormRopeArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = a.nqh + (a.value_is_key ? a.nkh : 2 * a.nkh);
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)a.rows * heads) return;
+    const int row = (int)(item / heads), head = (int)(item - (long long)row * heads);
+    const int seq = a.token_seq[row];
+    if (seq < 0) return;
+    const int pos = a.positions[row];
+    const bool is_q = head < a.nqh, is_k = !is_q && head < a.nqh + a.nkh;
+    T* src = (T*)a.qk + (size_t)row * a.row_stride + (size_t)head * a.hd;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (!is_q && a.cache) {
+        const int kvh = is_k ? head - a.nqh : head - a.nqh - a.nkh;
+        const int block = pos / a.page_size, off = pos - block * a.page_size;
+        int page = (block < a.table_cols) ? a.page_table[(size_t)seq * a.table_cols + block] : -1;
+        if (page < 0 || page >= a.num_pages) {
+            if (lane == 0) atomicExch(a.error_flag, 1);
+        } else {
+            T* kplane = (T*)a.cache + ((((size_t)page * 2) * a.nkh + kvh) * a.page_size + off) * a.hd;
+            T* vplane = kplane + (size_t)a.nkh * a.page_size * a.hd;
+            if (is_k) { kdst = kplane; if (a.value_is_key) vdst = vplane; }
+            else vdst = vplane;
+        }
+    }
+    constexpr int PER = HEAD_NORM_MAX_HD / 32;
+    float x[PER];
+    // element e of this lane is head element 2 * (lane + 32 * (e / 2)) + (e & 1): a lane holds whole adjacent pairs
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
+        x[e] = i < a.hd ? to_f32(src[i]) : 0.f;
+        ss = fmaf(x[e], x[e], ss);
+    }
+    if (vdst) {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
+            if (i < a.hd) vdst[i] = from_f32<T>(x[e]);
+        }
+    }
+    if (!is_q && !is_k) return;
+    const void* wv = is_q ? a.q_w : a.k_w;
+    if (wv) {
+        ss = warp_sum(ss);
+        const float r = 1.f / sqrtf(ss / (float)a.hd + a.eps);
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
+            if (i < a.hd) x[e] = x[e] * r * to_f32(((const T*)wv)[i]);
+        }
+    }
+    const int half = a.rope_dim / 2;
+    if (a.adjacent) {
+#pragma unroll
+        for (int e = 0; e < PER; e += 2) {
+            const int p = lane + 32 * (e >> 1);
+            if (p < half) {
+                float sn, cs;
+                sincosf((float)pos * a.inv_freq[p], &sn, &cs);
+                sn *= a.amp; cs *= a.amp;
+                const float u = x[e], v = x[e + 1];
+                x[e] = u * cs - v * sn;
+                x[e + 1] = v * cs + u * sn;
+            }
+        }
+    } else if (half > 0) {
+        // pairs (p, p + half) lie in different lanes: through shared memory
+        __shared__ float stage[4][HEAD_NORM_MAX_HD];
+        float* st = stage[warp];
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
+            if (i < a.hd) st[i] = x[e];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
+            if (i < a.rope_dim) {
+                const int p = i < half ? i : i - half;
+                float sn, cs;
+                sincosf((float)pos * a.inv_freq[p], &sn, &cs);
+                sn *= a.amp; cs *= a.amp;
+                x[e] = i < half ? st[i] * cs - st[i + half] * sn : st[i] * cs + st[i - half] * sn;
+            }
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
+        if (i < a.hd) {
+            const T y = from_f32<T>(x[e]);
+            src[i] = y;
+            if (kdst) kdst[i] = y;
+        }
+    }
+}
+
+extern "C" int braid_head_norm_rope_kv(void* qk, long long row_stride, int dtype, const void* q_w, const void* k_w,
+                                       const float* inv_freq, const int* positions, const int* token_seq,
+                                       const int* page_table, void* cache, int rows, int nqh, int nkh, int hd,
+                                       int rope_dim, int adjacent, int value_is_key, int page_size, int table_cols,
+                                       int num_pages, float eps, float amp, int* error_flag, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (nqh <= 0 || nkh <= 0 || hd <= 0 || hd > HEAD_NORM_MAX_HD || (hd & 1))
+        BRAID_REFUSE("head_norm_rope_kv: heads must be positive and head_dim=%d even and at most %d", hd, HEAD_NORM_MAX_HD);
+    if (rope_dim < 0 || rope_dim > hd || (rope_dim & 1)) BRAID_REFUSE("head_norm_rope_kv: rope_dim=%d must be even and <= head_dim=%d", rope_dim, hd);
+    HeadNormRopeArgs a{qk, row_stride, q_w, k_w, inv_freq, positions, token_seq, page_table, cache, rows, nqh, nkh, hd,
+                       rope_dim, adjacent, value_is_key, page_size, table_cols, num_pages, eps, amp, error_flag};
+    const long long items = (long long)rows * (nqh + (value_is_key ? nkh : 2 * nkh));
+    const long long blocks = (items + 3) / 4;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("head_norm_rope_kv: %lld (row, head) pairs exceed one launch", items);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32) braid_launch(head_norm_rope_kv_kernel<float>, dim3((int)blocks), dim3(128), 0, s, a);
+    else if (dtype == BRAID_BF16) braid_launch(head_norm_rope_kv_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(128), 0, s, a);
+    else BRAID_REFUSE("head_norm_rope_kv: unknown dtype code %d", dtype);
     BRAID_LAUNCH_CHECK();
 }
 

@@ -63,6 +63,7 @@ struct GemmTcArgs {
     int tile_begin, tile_end;  // the tiles of the walk (tc_tile_coords) that this launch covers
     RowScaleArgs scale;        // modes 0, 2: a row scale of the tokens, or none; mode 3: see rs_out
     float* rs_out;             // mode 3 with a scale: CTA 0 writes the scale of every row here, for the kernel that adds up
+    int act;                   // mode 2: the gate's activation (BRAID_ACT_*)
 };
 
 template <int BLOCK_N, int MODE>
@@ -325,10 +326,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const float from_gate = __shfl_xor_sync(0xffffffffu, v[2 * p2 + 1], 16);  // up lanes get gate's value
                         const float g = is_up ? from_gate : v[2 * p2];
                         const float u = is_up ? v[2 * p2 + 1] : from_up;
-                        // silu(g) * u with the fast exponential and division: a few ulp, far inside
-                        // the bfloat16 rounding of the result, and no slow path for the infinities
-                        // that exp(-g) reaches (g / inf = 0 is the right limit)
-                        const float y = __fdividef(g, 1.f + __expf(-g)) * u;
+                        const float y = glu_act_fast(g, a.act) * u;
                         const int n = t.n0 + c0 + 2 * p2 + (is_up ? 1 : 0);
                         if (m < a.m_out && n < a.n_rows) {
                             if (a.out_dtype == BRAID_F32) ((float*)a.out)[o0 + (size_t)(2 * p2) * a.ldo] = y;
@@ -390,7 +388,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // token; threads are laid over the line's tiles.
 template <int MODE>
 __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const float* __restrict__ res,
-                                      int m_out, long long ldo, int out_dtype, const float* __restrict__ rs_rows) {
+                                      int m_out, long long ldo, int out_dtype, const float* __restrict__ rs_rows, int act) {
     pdl_trigger();
     constexpr int GROUPS = (MODE == 2) ? 16 : 32;          // groups of four outputs that a tile holds per token
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -416,10 +414,10 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
         streamk_sum4_pair(k, sp, n, c0, c0 + 16, g4, u4);
         g4.x *= rs; g4.y *= rs; g4.z *= rs; g4.w *= rs;
         u4.x *= rs; u4.y *= rs; u4.z *= rs; u4.w *= rs;
-        v[0] = g4.x / (1.f + expf(-g4.x)) * u4.x;
-        v[1] = g4.y / (1.f + expf(-g4.y)) * u4.y;
-        v[2] = g4.z / (1.f + expf(-g4.z)) * u4.z;
-        v[3] = g4.w / (1.f + expf(-g4.w)) * u4.w;
+        v[0] = glu_act(g4.x, act) * u4.x;
+        v[1] = glu_act(g4.y, act) * u4.y;
+        v[2] = glu_act(g4.z, act) * u4.z;
+        v[3] = glu_act(g4.w, act) * u4.w;
     } else {
         const float4 s4 = streamk_sum4(k, sp, n, c0);
         v[0] = s4.x * rs; v[1] = s4.y * rs; v[2] = s4.z * rs; v[3] = s4.w * rs;
@@ -435,15 +433,15 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
 }
 
 static int launch_streamk_reduce(const StreamK& k, void* out, const float* res, int m_out, long long ldo, int out_dtype,
-                                 int mode, const float* rs_rows, cudaStream_t s) {
+                                 int mode, const float* rs_rows, cudaStream_t s, int act = BRAID_ACT_SILU) {
     const long long tiles = k.w / k.total_kb;
     const long long total = tiles * k.block_n * (mode == 2 ? 16 : 32);
     const int threads = 128;
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("streamk_reduce: %lld outputs exceed one launch", total);
-    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, rs_rows);
-    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, rs_rows);
-    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, rs_rows);
+    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, rs_rows, act);
+    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, rs_rows, act);
+    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, rs_rows, act);
     BRAID_LAUNCH_CHECK();
 }
 
@@ -545,7 +543,10 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
                              int* plan_out, const float* scale_shares, int scale_n_shares, long long scale_stride,
                              float scale_width, float scale_eps, float* rs_rows, int* error_flag, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
+    const int act = (mode >> 4) & 15;                    // the activation of a gated epilogue rides in bits 4..7
+    mode &= 15;
     if (mode < 0 || mode > 2) BRAID_REFUSE("gemm_tc: unknown epilogue %d", mode);
+    if (act >= BRAID_ACT_COUNT || (act && mode != 2)) BRAID_REFUSE("gemm_tc: unknown activation %d for epilogue %d", act, mode);
     if (k_in <= 0) BRAID_REFUSE("gemm_tc: k=%d must be positive", k_in);
     if ((ldx % 8) || (ldw % 8)) BRAID_REFUSE("gemm_tc: row strides (%lld, %lld) must be multiples of 8 elements for TMA", ldx, ldw);
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) BRAID_REFUSE("gemm_tc: operands must be 16-byte aligned for TMA");
@@ -583,7 +584,7 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     if (stream_k) p = plan_stream_k(n_rows, w_rows, k_in, block_n);
     const int whole_end = stream_k ? p.tile_begin : all_tiles;       // tiles [0, whole_end) run as whole tiles
     if (whole_end > 0) {
-        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag, 0, whole_end, scale, nullptr};
+        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag, 0, whole_end, scale, nullptr, act};
         dim3 grid((unsigned)(whole_end < sm_count() ? whole_end : sm_count()), 1, 1);
         if (mode == 0) rc = dispatch_tc<0>(block_n, mw, mx, a, grid, s);
         else if (mode == 1) rc = dispatch_tc<1>(block_n, mw, mx, a, grid, s);
@@ -592,7 +593,7 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     }
     if (!stream_k || p.tiles == 0) return BRAID_OK;
     GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, p.m_tiles, p.n_tiles, p.max_segs, error_flag,
-                 p.tile_begin, p.tile_begin + p.tiles, scale, scale.shares ? rs_rows : nullptr};
+                 p.tile_begin, p.tile_begin + p.tiles, scale, scale.shares ? rs_rows : nullptr, act};
     rc = dispatch_tc<3>(block_n, mw, mx, a, dim3(p.grid, 1, 1), s);
     if (rc) return rc;
     if (plan_out) {
@@ -602,16 +603,19 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
         return BRAID_OK;
     }
     StreamK k{(const float*)workspace, p.grid, p.max_segs, p.total_kb, p.n_tiles, n_rows, block_n, p.w, p.m_tiles, p.tile_begin};
-    return launch_streamk_reduce(k, out, res, m_out, ldo, out_dtype, mode, scale.shares ? rs_rows : nullptr, s);
+    return launch_streamk_reduce(k, out, res, m_out, ldo, out_dtype, mode, scale.shares ? rs_rows : nullptr, s, act);
 }
 
 // Add up the partial products of an earlier stream-k call made with plan_out (the same
-// reduce the fused call runs): mode 0 store, 1 res + sum, 2 silu(gate) * up.
+// reduce the fused call runs): mode 0 store, 1 res + sum, 2 act(gate) * up (the activation's code in bits 4..7 of mode).
 extern "C" int braid_streamk_reduce(const float* partial, const int* plan, int n_rows, void* out, const float* res,
                                     int m_out, long long ldo, int out_dtype, int mode, const float* rs_rows, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
+    const int act = (mode >> 4) & 15;
+    mode &= 15;
     if (mode < 0 || mode > 2) BRAID_REFUSE("streamk_reduce: unknown epilogue %d", mode);
+    if (act >= BRAID_ACT_COUNT || (act && mode != 2)) BRAID_REFUSE("streamk_reduce: unknown activation %d for epilogue %d", act, mode);
     if (mode == 1 && (!res || out_dtype != BRAID_F32)) BRAID_REFUSE("streamk_reduce: the residual epilogue writes float32 and needs res");
     if (rs_rows && mode == 1) BRAID_REFUSE("streamk_reduce: the residual epilogue takes no row scale");
-    return launch_streamk_reduce(streamk_from_plan(partial, plan, n_rows), out, res, m_out, ldo, out_dtype, mode, rs_rows, (cudaStream_t)stream);
+    return launch_streamk_reduce(streamk_from_plan(partial, plan, n_rows), out, res, m_out, ldo, out_dtype, mode, rs_rows, (cudaStream_t)stream, act);
 }

@@ -53,6 +53,7 @@ struct GemmTc2Args {
     int out_dtype;
     int m_tiles, n_tiles;      // tiles of 256 weight rows x 256 tokens
     int* error_flag;
+    int act;                   // mode 2: the gate's activation (BRAID_ACT_*)
 };
 
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
@@ -277,7 +278,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                             const float from_gate = __shfl_xor_sync(0xffffffffu, v[2 * p2 + 1], 16);
                             const float g = is_up ? from_gate : v[2 * p2];
                             const float u = is_up ? v[2 * p2 + 1] : from_up;
-                            dst[2 * p2 * 64] = __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+                            dst[2 * p2 * 64] = __float2bfloat16_rn(glu_act_fast(g, a.act) * u);
                         }
                     } else if (a.out_dtype == BRAID_F32) {
                         float* dst = (float*)tile + quarter * 32 + lane;
@@ -309,7 +310,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         const float from_gate = __shfl_xor_sync(0xffffffffu, v[2 * p2 + 1], 16);
                         const float g = is_up ? from_gate : v[2 * p2];
                         const float u = is_up ? v[2 * p2 + 1] : from_up;
-                        const float y = __fdividef(g, 1.f + __expf(-g)) * u;
+                        const float y = glu_act_fast(g, a.act) * u;
                         const int n = t.n0 + c0 + 2 * p2 + (is_up ? 1 : 0);
                         if (m < a.m_out && n < a.n_rows) {
                             if (a.out_dtype == BRAID_F32) ((float*)a.out)[o0 + (size_t)(2 * p2) * a.ldo] = y;
@@ -417,7 +418,10 @@ extern "C" int braid_gemm_tc2(const void* x, const void* w, void* out, const flo
                               int n_rows, int m_out, int k_in, long long ldx, long long ldw, long long ldo,
                               int direct_out, int* error_flag, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
+    const int act = (mode >> 4) & 15;                    // the activation of a gated epilogue rides in bits 4..7
+    mode &= 15;
     if (mode < 0 || mode > 2) BRAID_REFUSE("gemm_tc2: unknown epilogue %d", mode);
+    if (act >= BRAID_ACT_COUNT || (act && mode != 2)) BRAID_REFUSE("gemm_tc2: unknown activation %d for epilogue %d", act, mode);
     if (k_in <= 0) BRAID_REFUSE("gemm_tc2: k=%d must be positive", k_in);
     if ((ldx % 8) || (ldw % 8)) BRAID_REFUSE("gemm_tc2: row strides (%lld, %lld) must be multiples of 8 elements for TMA", ldx, ldw);
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) BRAID_REFUSE("gemm_tc2: operands must be 16-byte aligned for TMA");
@@ -447,7 +451,7 @@ extern "C" int braid_gemm_tc2(const void* x, const void* w, void* out, const flo
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 1) sms = 148;
     const long long units = (long long)m_tiles * n_tiles;
     const int pairs = (int)(units < sms / 2 ? units : sms / 2);
-    GemmTc2Args a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, error_flag};
+    GemmTc2Args a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, error_flag, act};
     cudaStream_t s = (cudaStream_t)stream;
     if (tma_out) {
         if (mode == 0) return launch_tc2<0, true>(mw, mx, mo, a, pairs, s);

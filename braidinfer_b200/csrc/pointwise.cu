@@ -91,3 +91,70 @@ extern "C" int braid_concat2(const float* a, const float* b, void* out, int out_
     else BRAID_REFUSE("concat2: unknown dtype code %d", out_dtype);
     BRAID_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------ a layer's own token input
+// g[r, j] = act(gate[r, j]) * table[token[r], col0 + j]: a gate computed from the stream, times the columns
+// [col0, col0 + dim) of a token table's row.  float32 arithmetic; gate, table and g in the run's type.
+template <typename T>
+__global__ void act_mul_gather_kernel(const T* __restrict__ gate, long long gate_stride, const T* __restrict__ table,
+                                      long long table_stride, const int* __restrict__ ids, int vocab, int col0,
+                                      T* __restrict__ out, long long total, int dim, int act) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long r = i / dim;
+    const int j = (int)(i - r * dim);
+    int id = ids[r];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const float g = to_f32(gate[r * gate_stride + j]);
+    out[i] = from_f32<T>(glu_act(g, act) * to_f32(table[(size_t)id * table_stride + col0 + j]));
+}
+
+extern "C" int braid_act_mul_gather(const void* gate, long long gate_stride, const void* table, long long table_stride,
+                                    const int* ids, int vocab, int col0, void* out, int dtype, int rows, int dim, int act,
+                                    void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (dim <= 0 || vocab <= 0 || col0 < 0) BRAID_REFUSE("act_mul_gather: dim=%d, vocab=%d, col0=%d", dim, vocab, col0);
+    if (act < 0 || act >= BRAID_ACT_COUNT) BRAID_REFUSE("act_mul_gather: unknown activation %d", act);
+    const long long total = (long long)rows * dim;
+    const int threads = 256;
+    const long long blocks = (total + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("act_mul_gather: %lld elements exceed one launch", total);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32)
+        braid_launch(act_mul_gather_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gate, gate_stride,
+                     (const float*)table, table_stride, ids, vocab, col0, (float*)out, total, dim, act);
+    else if (dtype == BRAID_BF16)
+        braid_launch(act_mul_gather_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gate,
+                     gate_stride, (const __nv_bfloat16*)table, table_stride, ids, vocab, col0, (__nv_bfloat16*)out, total, dim, act);
+    else BRAID_REFUSE("act_mul_gather: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// h[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w: an RMS norm (plain weight) of a branch's result, added to the float32
+// stream.  y float32 [rows, width]; one CTA a row; sums in float32, the same order every time.
+template <typename TW>
+__global__ void __launch_bounds__(256)
+rmsnorm_add_kernel(float* __restrict__ h, const float* __restrict__ y, const TW* __restrict__ w, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[32];
+    const size_t base = (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) { const float v = y[base + c]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float r = 1.f / sqrtf(ss / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) h[base + c] += y[base + c] * r * to_f32(w[c]);
+}
+
+extern "C" int braid_rmsnorm_add(float* h, const float* y, const void* w, int w_dtype, int rows, int width, float eps,
+                                 void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (width <= 0) BRAID_REFUSE("rmsnorm_add: width=%d must be positive", width);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w_dtype == BRAID_F32) braid_launch(rmsnorm_add_kernel<float>, dim3(rows), dim3(256), 0, s, h, y, (const float*)w, width, eps);
+    else if (w_dtype == BRAID_BF16) braid_launch(rmsnorm_add_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, s, h, y, (const __nv_bfloat16*)w, width, eps);
+    else BRAID_REFUSE("rmsnorm_add: unknown dtype code %d", w_dtype);
+    BRAID_LAUNCH_CHECK();
+}

@@ -1,0 +1,326 @@
+// Kernels of mixers that carry a fixed-size state from token to token instead of keys and values:
+// a short causal convolution per channel, the linear recurrence S_t = diag(a_t) S_(t-1) + k_t v_t^T
+// with o_t = S_t^T q_t (gated linear attention: a decay per key channel; state-space duality: one
+// decay per head, a step size on the key and a skip term), and the gated RMS norms that follow them.
+//
+// A step's rows are packed sequence after sequence (q_start, q_len per sequence; a row's token_seq
+// is its sequence or -1 for padding).  The state of a sequence lies in its slot of the cache's state
+// area: `state` + slot * state_stride bytes; every kernel below is given the byte offset of its own
+// part of it.  The state, the decays, step sizes, gates and norms are float32 whatever the run's
+// element type; projections and the convolution's output are in the run's type T.
+//
+// A recurrence is walked token by token in the order of the sequence, so the state after a prompt
+// does not depend on how the prompt was cut into steps: a step continues from the stored state with
+// the very operations a longer step would have done.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ causal convolution
+// y[t, c] = act(b[c] + sum_j w[c, j] x[t - (taps - 1 - j), c]): the last column of w is the current
+// token's.  Inputs before the step come from the state, which keeps a sequence's last taps - 1
+// inputs (zeros before its start): state[i, c], i = taps - 2 the newest.
+struct ConvArgs {
+    const void* x;               // [rows, x_stride], channel c at column c
+    long long x_stride;
+    void* y;                     // [rows, y_stride]
+    long long y_stride;
+    const void* w;               // [channels, taps]
+    const void* b;               // [channels] or null
+    uint8_t* state;
+    long long state_stride, state_offset;
+    const int* token_seq;
+    const int* q_start;
+    const int* slot_ids;
+    int rows, channels, taps, silu;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+causal_conv_kernel(ConvArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int row = blockIdx.y;
+    if (c >= a.channels) return;
+    const int seq = a.token_seq[row];
+    if (seq < 0) return;
+    const int o = row - a.q_start[seq];
+    const float* st = (const float*)(a.state + (size_t)a.slot_ids[seq] * a.state_stride + a.state_offset);
+    float acc = a.b ? to_f32(((const T*)a.b)[c]) : 0.f;
+    for (int j = 0; j < a.taps; ++j) {
+        const int back = a.taps - 1 - j;
+        float xv;
+        if (o - back >= 0) xv = to_f32(((const T*)a.x)[(size_t)(row - back) * a.x_stride + c]);
+        else xv = st[(size_t)(a.taps - 1 + (o - back)) * a.channels + c];
+        acc = fmaf(to_f32(((const T*)a.w)[(size_t)c * a.taps + j]), xv, acc);
+    }
+    if (a.silu) acc = silu_f32(acc);
+    ((T*)a.y)[(size_t)row * a.y_stride + c] = from_f32<T>(acc);
+}
+
+// The state after the step: the sequence's last taps - 1 inputs.  One thread per (sequence, channel)
+// reads what it needs of the old state before it writes (entry i takes old entry i + n, n the step's
+// tokens of the sequence, or a row of the step), in rising i: no other thread touches its column.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_state_kernel(ConvArgs a, const int* __restrict__ q_len, int n_seqs) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int seq = blockIdx.y;
+    if (c >= a.channels || seq >= n_seqs) return;
+    const int n = q_len[seq], r0 = a.q_start[seq];
+    float* st = (float*)(a.state + (size_t)a.slot_ids[seq] * a.state_stride + a.state_offset);
+    const int keep = a.taps - 1;
+    for (int i = 0; i < keep; ++i) {
+        const int o = n - keep + i;                  // the step's token that entry i holds, if not negative
+        float v;
+        if (o >= 0) v = to_f32(((const T*)a.x)[(size_t)(r0 + o) * a.x_stride + c]);
+        else v = st[(size_t)(i + n) * a.channels + c];
+        st[(size_t)i * a.channels + c] = v;
+    }
+}
+
+extern "C" int braid_causal_conv(const void* x, long long x_stride, void* y, long long y_stride, const void* w, const void* b,
+                                 int dtype, void* state, long long state_stride, long long state_offset,
+                                 const int* token_seq, const int* q_start, const int* q_len, const int* slot_ids,
+                                 int rows, int n_seqs, int channels, int taps, int silu, void* stream) {
+    if (rows <= 0 || n_seqs <= 0) return BRAID_OK;
+    if (channels <= 0 || taps < 1) BRAID_REFUSE("causal_conv: channels=%d and taps=%d must be positive", channels, taps);
+    if (!state || (state_offset & 3) || (state_stride & 3)) BRAID_REFUSE("causal_conv: the state area must be given, in multiples of 4 bytes");
+    if (rows > 65535 * 16 || n_seqs > 65535) BRAID_REFUSE("causal_conv: the step exceeds the grid limits");
+    ConvArgs a{x, x_stride, y, y_stride, w, b, (uint8_t*)state, state_stride, state_offset, token_seq, q_start, slot_ids,
+               rows, channels, taps, silu};
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    dim3 g1((channels + threads - 1) / threads, rows), g2((channels + threads - 1) / threads, n_seqs);
+    if (g1.y > 65535) BRAID_REFUSE("causal_conv: %d rows exceed one launch", rows);
+    if (dtype == BRAID_F32) {
+        braid_launch(causal_conv_kernel<float>, g1, dim3(threads), 0, s, a);
+        if (taps > 1) braid_launch(conv_state_kernel<float>, g2, dim3(threads), 0, s, a, q_len, n_seqs);
+    } else if (dtype == BRAID_BF16) {
+        braid_launch(causal_conv_kernel<__nv_bfloat16>, g1, dim3(threads), 0, s, a);
+        if (taps > 1) braid_launch(conv_state_kernel<__nv_bfloat16>, g2, dim3(threads), 0, s, a, q_len, n_seqs);
+    } else BRAID_REFUSE("causal_conv: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ the linear recurrence
+// Per sequence and head, token by token:  S <- diag(a_t) S + (kappa_t k_t) v_t^T,  o_t = S^T (q_scale q_t) + skip * v_t.
+// S is [dk, dv] float32 in the sequence's state.
+//   DECAY_CHANNEL (gated linear attention): a_t[i] = sigmoid(z_t[h, i] + zb[h, i])^(1 / tau), kappa = 1, no skip;
+//       z float32 [rows, heads * dk].
+//   DECAY_HEAD (state-space duality): dt = softplus(d_t[h] + dt_bias[h]), a_t = exp(-exp(A_log[h]) dt) for every
+//       channel, kappa = dt, skip = D[h]; d in the run's type [rows, heads] (row stride gate_stride).
+// q and k: [rows, groups, dk] in the run's type (head h reads group h / (heads / groups)); v: [rows, heads, dv].
+// out: float32 [rows, heads * dv].
+//
+// A CTA owns (head, sequence, a tile of SCAN_DV value columns); thread (j, s) keeps dk / SCAN_KS
+// rows of column j of S in registers (rows s, s + KS, ...).  Tokens are staged SCAN_TB at a time in shared memory
+// (q, k, decay, v), so the walk itself has no block-wide barrier per token: the KS partial sums of a
+// column meet by warp shuffles.
+#define SCAN_DV 32
+#define SCAN_KS 4
+#define SCAN_TB 8
+#define SCAN_MAX_DK 256
+#define DECAY_CHANNEL 0
+#define DECAY_HEAD 1
+
+struct ScanArgs {
+    const void* q; long long q_stride;
+    const void* k; long long k_stride;
+    const void* v; long long v_stride;
+    const void* gate; long long gate_stride;   // z (float32) or d (run type)
+    const void* gate_bias;       // zb [heads * dk] or dt_bias [heads], run type
+    const void* a_log;           // [heads], run type (DECAY_HEAD)
+    const void* skip;            // [heads], run type, or null
+    float* out; long long out_stride;
+    uint8_t* state; long long state_stride, state_offset;
+    const int* q_start; const int* q_len; const int* slot_ids;
+    int heads, groups, dk, dv;
+    float q_scale, inv_tau;
+};
+
+template <typename T, int MODE, int MAX_DK>
+__global__ void __launch_bounds__(SCAN_DV * SCAN_KS)
+linear_scan_kernel(ScanArgs a) {
+    pdl_trigger();
+    const int h = blockIdx.x, seq = blockIdx.y, j0 = blockIdx.z * SCAN_DV;
+    const int tid = threadIdx.x;
+    const int ks = tid % SCAN_KS, jl = tid / SCAN_KS;       // the KS threads of a column are neighbours in a warp
+    const int j = j0 + jl;
+    const int n = a.q_len[seq], r0 = a.q_start[seq];
+    if (n <= 0) return;
+    constexpr int PER = MAX_DK / SCAN_KS;                  // rows of S a thread keeps
+    const int dk = a.dk;
+    const int g = h / (a.heads / a.groups);
+    extern __shared__ float sm[];                           // [TB][3][dk] q, k, decay; [TB][SCAN_DV] v; [TB] kappa
+    float* sq = sm;
+    float* sk = sm + SCAN_TB * dk;
+    float* sa = sm + 2 * SCAN_TB * dk;
+    float* sv = sm + 3 * SCAN_TB * dk;
+    float* skap = sv + SCAN_TB * SCAN_DV;
+    float head_a = 0.f, head_bias = 0.f, head_skip = 0.f;
+    if (MODE == DECAY_HEAD) {
+        head_a = -expf(to_f32(((const T*)a.a_log)[h]));
+        head_bias = to_f32(((const T*)a.gate_bias)[h]);
+        if (a.skip) head_skip = to_f32(((const T*)a.skip)[h]);
+    }
+    pdl_wait();
+    float* S = (float*)(a.state + (size_t)a.slot_ids[seq] * a.state_stride + a.state_offset) + (size_t)h * dk * a.dv;
+    float s[PER];
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        const int i = ks + e * SCAN_KS;
+        s[e] = (i < dk && j < a.dv) ? S[(size_t)i * a.dv + j] : 0.f;
+    }
+    for (int t0 = 0; t0 < n; t0 += SCAN_TB) {
+        const int nt = min(SCAN_TB, n - t0);
+        __syncthreads();                                    // the batch before has been read
+        for (int idx = tid; idx < nt * dk; idx += blockDim.x) {
+            const int t = idx / dk, i = idx - t * dk;
+            const size_t row = (size_t)(r0 + t0 + t);
+            sq[t * dk + i] = to_f32(((const T*)a.q)[row * a.q_stride + (size_t)g * dk + i]) * a.q_scale;
+            sk[t * dk + i] = to_f32(((const T*)a.k)[row * a.k_stride + (size_t)g * dk + i]);
+            if (MODE == DECAY_CHANNEL) {
+                const float z = ((const float*)a.gate)[row * a.gate_stride + (size_t)h * dk + i] +
+                                to_f32(((const T*)a.gate_bias)[(size_t)h * dk + i]);
+                // log sigmoid(z) = -softplus(-z) = min(z, 0) - log1p(exp(-|z|))
+                const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+                sa[t * dk + i] = expf(ls * a.inv_tau);
+            }
+        }
+        for (int idx = tid; idx < nt * SCAN_DV; idx += blockDim.x) {
+            const int t = idx / SCAN_DV, jj = idx - t * SCAN_DV;
+            const size_t row = (size_t)(r0 + t0 + t);
+            sv[idx] = (j0 + jj < a.dv) ? to_f32(((const T*)a.v)[row * a.v_stride + (size_t)h * a.dv + j0 + jj]) : 0.f;
+        }
+        if (MODE == DECAY_HEAD && tid < nt) {
+            const size_t row = (size_t)(r0 + t0 + tid);
+            const float x = to_f32(((const T*)a.gate)[row * a.gate_stride + h]) + head_bias;
+            const float dt = x > 20.f ? x : log1pf(expf(x));           // softplus
+            skap[tid] = dt;
+            sa[tid] = expf(head_a * dt);
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float vj = sv[t * SCAN_DV + jl];
+            const float kap = (MODE == DECAY_HEAD) ? skap[t] : 1.f;
+            const float ah = (MODE == DECAY_HEAD) ? sa[t] : 0.f;
+            const float kv = kap * vj;
+            float acc = 0.f;
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                const int i = ks + e * SCAN_KS;
+                if (i < dk) {
+                    const float dec = (MODE == DECAY_HEAD) ? ah : sa[t * dk + i];
+                    s[e] = fmaf(dec, s[e], sk[t * dk + i] * kv);
+                    acc = fmaf(s[e], sq[t * dk + i], acc);
+                }
+            }
+#pragma unroll
+            for (int o = SCAN_KS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (ks == 0 && j < a.dv)
+                a.out[(size_t)(r0 + t0 + t) * a.out_stride + (size_t)h * a.dv + j] = acc + head_skip * vj;
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        const int i = ks + e * SCAN_KS;
+        if (i < dk && j < a.dv) S[(size_t)i * a.dv + j] = s[e];
+    }
+}
+
+extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
+                                 long long v_stride, const void* gate, long long gate_stride, const void* gate_bias,
+                                 const void* a_log, const void* skip, float* out, long long out_stride, void* state,
+                                 long long state_stride, long long state_offset, const int* q_start, const int* q_len,
+                                 const int* slot_ids, int dtype, int mode, int n_seqs, int heads, int groups, int dk, int dv,
+                                 float q_scale, float inv_tau, void* stream) {
+    if (n_seqs <= 0) return BRAID_OK;
+    if (heads <= 0 || groups <= 0 || heads % groups) BRAID_REFUSE("linear_scan: %d heads do not divide into %d groups", heads, groups);
+    if (dk <= 0 || dk > SCAN_MAX_DK || dv <= 0) BRAID_REFUSE("linear_scan: key size %d must be in (0, %d], value size %d positive", dk, SCAN_MAX_DK, dv);
+    if (!state || (state_offset & 3) || (state_stride & 3)) BRAID_REFUSE("linear_scan: the state area must be given, in multiples of 4 bytes");
+    if (mode != DECAY_CHANNEL && mode != DECAY_HEAD) BRAID_REFUSE("linear_scan: unknown decay mode %d", mode);
+    if (mode == DECAY_HEAD && !a_log) BRAID_REFUSE("linear_scan: a decay per head needs A_log");
+    if (n_seqs > 65535 || (dv + SCAN_DV - 1) / SCAN_DV > 65535) BRAID_REFUSE("linear_scan: the step exceeds the grid limits");
+    ScanArgs a{q, q_stride, k, k_stride, v, v_stride, gate, gate_stride, gate_bias, a_log, skip, out, out_stride,
+               (uint8_t*)state, state_stride, state_offset, q_start, q_len, slot_ids, heads, groups, dk, dv, q_scale, inv_tau};
+    dim3 grid(heads, n_seqs, (dv + SCAN_DV - 1) / SCAN_DV);
+    const size_t smem = (size_t)(3 * SCAN_TB * dk + SCAN_TB * SCAN_DV + SCAN_TB) * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 block(SCAN_DV * SCAN_KS);
+    if (dtype != BRAID_F32 && dtype != BRAID_BF16) BRAID_REFUSE("linear_scan: unknown dtype code %d", dtype);
+    // the kernel is compiled for key sizes up to 64, 128 and 256: a thread keeps a quarter of a column's rows in registers
+#define SCAN_LAUNCH(TT, MM)                                                                                   \
+    do {                                                                                                      \
+        if (dk <= 64) braid_launch(linear_scan_kernel<TT, MM, 64>, grid, block, smem, s, a);                  \
+        else if (dk <= 128) braid_launch(linear_scan_kernel<TT, MM, 128>, grid, block, smem, s, a);           \
+        else braid_launch(linear_scan_kernel<TT, MM, 256>, grid, block, smem, s, a);                          \
+    } while (0)
+    if (dtype == BRAID_F32 && mode == DECAY_CHANNEL) SCAN_LAUNCH(float, DECAY_CHANNEL);
+    else if (dtype == BRAID_F32) SCAN_LAUNCH(float, DECAY_HEAD);
+    else if (mode == DECAY_CHANNEL) SCAN_LAUNCH(__nv_bfloat16, DECAY_CHANNEL);
+    else SCAN_LAUNCH(__nv_bfloat16, DECAY_HEAD);
+#undef SCAN_LAUNCH
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ gated RMS norm
+// y [rows, width] float32 (a recurrence's output), gate [rows, gate_stride] in the run's type, in groups of `group`
+// columns, each normed by its own root mean square:
+//   gate_first = 0:  out = y / rms(y) * w * silu(gate) * out_scale         (norm, then gate)
+//   gate_first = 1:  u = y * silu(gate);  out = u / rms(u) * w * out_scale (gate, then norm)
+// w has w_len numbers; column c of the row reads w[c % w_len] (w_len = group: one weight for every group;
+// w_len = width: a weight per column).  One warp per (row, group).  Everything in float32; out in the run's type.
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate, long long gate_stride, const T* __restrict__ w,
+                  int w_len, T* __restrict__ out, long long out_stride, const int* __restrict__ token_seq, int rows,
+                  int width, int group, int gate_first, float eps, float out_scale) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int groups = width / group;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)rows * groups) return;
+    const int row = (int)(item / groups), gi = (int)(item - (long long)row * groups);
+    if (token_seq[row] < 0) return;
+    const float* yr = y + (size_t)row * width + (size_t)gi * group;
+    const T* gr = gate + (size_t)row * gate_stride + (size_t)gi * group;
+    float ss = 0.f;
+    for (int c = lane; c < group; c += 32) {
+        float u = yr[c];
+        if (gate_first) u *= silu_f32(to_f32(gr[c]));
+        ss = fmaf(u, u, ss);
+    }
+    ss = warp_sum(ss);
+    const float r = 1.f / sqrtf(ss / (float)group + eps);
+    T* orow = out + (size_t)row * out_stride + (size_t)gi * group;
+    for (int c = lane; c < group; c += 32) {
+        const float sg = silu_f32(to_f32(gr[c]));
+        const float wv = to_f32(w[(gi * group + c) % w_len]);
+        float u = yr[c];
+        u = gate_first ? (u * sg) * r * wv : (u * r * wv) * sg;
+        orow[c] = from_f32<T>(u * out_scale);
+    }
+}
+
+extern "C" int braid_gated_norm(const float* y, const void* gate, long long gate_stride, const void* w, int w_len, void* out,
+                                long long out_stride, const int* token_seq, int dtype, int rows, int width, int group,
+                                int gate_first, float eps, float out_scale, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (width <= 0 || group <= 0 || width % group) BRAID_REFUSE("gated_norm: width %d is not a whole number of groups of %d", width, group);
+    if (w_len <= 0) BRAID_REFUSE("gated_norm: the weight has no numbers");
+    const long long items = (long long)rows * (width / group);
+    const long long blocks = (items + 3) / 4;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("gated_norm: %lld (row, group) pairs exceed one launch", items);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32)
+        braid_launch(gated_norm_kernel<float>, dim3((int)blocks), dim3(128), 0, s, y, (const float*)gate, gate_stride, (const float*)w,
+                     w_len, (float*)out, out_stride, token_seq, rows, width, group, gate_first, eps, out_scale);
+    else if (dtype == BRAID_BF16)
+        braid_launch(gated_norm_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(128), 0, s, y, (const __nv_bfloat16*)gate, gate_stride,
+                     (const __nv_bfloat16*)w, w_len, (__nv_bfloat16*)out, out_stride, token_seq, rows, width, group, gate_first, eps, out_scale);
+    else BRAID_REFUSE("gated_norm: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}

@@ -14,7 +14,7 @@ import torch
 
 from ..cache import CacheError, CacheManager, PAGE_SIZE
 from ..config import read_config_json
-from ..models import DecoderModel, architecture_for
+from ..models import DecoderModel, architecture_for, complete_config
 from ..parts.runtime import Runtime
 from ..weights import draw_tensors, load_tensors, tensor_specs_of
 from .step import StepContext, StepPacker
@@ -93,8 +93,10 @@ class Engine:
     # ------------------------------------------------------------------ construction
     @classmethod
     def from_folder(cls, folder: str, **kw) -> "Engine":
-        """A model folder: config.json picks the architecture, safetensors hold the weights."""
-        return cls(read_config_json(folder), folder, **kw)
+        """A model folder: config.json picks the architecture, safetensors hold the weights (and, for a design
+        that leaves a size to a tensor's shape, that size)."""
+        from ..weights.safetensors_io import tensor_shapes
+        return cls(complete_config(read_config_json(folder), tensor_shapes(folder)), folder, **kw)
 
     @classmethod
     def from_spec(cls, spec, seed: int = 0, *, dtype="bfloat16", device: str = "cuda:0", scale=None, **kw) -> "Engine":

@@ -9,7 +9,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts.base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, MIXERS, NORMS
+from ..parts.base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, LAYER_INPUTS, MIXERS, NORMS
 from ..parts.spec import CacheRequest, ModelSpec, TensorSpec
 
 
@@ -27,7 +27,10 @@ class DecoderModel:
             if ls.feed_forward is not None:
                 ffn = FEED_FORWARDS.get(ls.feed_forward.kind)(ls.feed_forward.params, ls.prefix, runtime)
                 ffn_norm = NORMS.get(ls.feed_forward_norm.kind)(ls.feed_forward_norm.params, ls.prefix, runtime)
-            self.blocks.append(BLOCKS.get(ls.block)(mixer, mixer_norm, ffn, ffn_norm))
+            block = BLOCKS.get(ls.block)(mixer, mixer_norm, ffn, ffn_norm)
+            if ls.layer_input is not None:
+                block.layer_input = LAYER_INPUTS.get(ls.layer_input.kind)(ls.layer_input.params, ls.prefix, runtime)
+            self.blocks.append(block)
         self.injection = None
         if spec.injection is not None:
             self.injection = INJECTIONS.get(spec.injection.kind)(spec.injection.params, "", runtime)

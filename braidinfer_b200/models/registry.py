@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Mapping
+from typing import Any, Callable, Dict, Mapping, Optional, Tuple
 
 from ..config.errors import ConfigError, UnknownArchitectureError
 from ..parts.spec import ModelSpec
@@ -14,10 +14,14 @@ class Architecture:
     only `build_spec` looks inside it); `build_spec` turns that configuration into a
     `ModelSpec`, the description of parts that everything else works from: loader, cache,
     step, generation, command line and replay read sizes, stop tokens and the longest
-    sequence from the `ModelSpec` alone."""
+    sequence from the `ModelSpec` alone.  `sizes_from_shapes` (optional) is for a design whose config.json
+    leaves a size to the shape of a stored tensor: given config.json's content and the folder's tensor shapes
+    (name -> shape) it returns the content with those sizes filled in; it runs before `config_from_dict`
+    wherever a model folder is opened (`complete_config`)."""
     name: str
     config_from_dict: Callable[[Mapping[str, Any]], Any]
     build_spec: Callable[[Any], ModelSpec]
+    sizes_from_shapes: Optional[Callable[[Mapping[str, Any], Mapping[str, Tuple[int, ...]]], Mapping[str, Any]]] = None
 
 
 ARCHITECTURES: Dict[str, Architecture] = {}
@@ -42,3 +46,11 @@ def architecture_for(config_dict: Mapping[str, Any]) -> Architecture:
             f"config.json names architecture '{name}', which is not registered; "
             f"known architectures: {sorted(ARCHITECTURES)}")
     return ARCHITECTURES[name]
+
+
+def complete_config(config_dict: Mapping[str, Any], shapes: Mapping[str, Tuple[int, ...]]) -> Mapping[str, Any]:
+    """config.json's content with the sizes that only tensor shapes give filled in (see `Architecture`)."""
+    arch = architecture_for(config_dict)
+    if arch.sizes_from_shapes is None:
+        return config_dict
+    return arch.sizes_from_shapes(config_dict, shapes)

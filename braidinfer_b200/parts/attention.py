@@ -6,6 +6,16 @@ into the cache -> attention over the cache -> output projection added to the res
 softmax in kernels/megakernel_ops.hip:2310-2342).  Head h reads kv head h // g.  Key j is
 visible to the query at position p iff j <= p and (no window or p - j < window); the
 reference has no window (crates/braidinfer-runtime/src/config.rs:416).
+
+Options that other designs use, each off unless named:
+    qk_norm         every query and key head is RMS-normed over the head, with a weight of head_dim numbers
+                    shared by the heads (plain weight), before the rotation
+    value_from_key  there is no value projection: a token's value is its key as projected, before norm and
+                    rotation (the cache then holds the rotated key and the raw one)
+    scale           the factor on the scores (default head_dim^-1/2)
+    sink            one more term exp(sink) in the softmax's denominator that has no value:
+                    p_j = exp(s_j) / (exp(sink) + sum_i exp(s_i)); a row may so give weight to nothing
+    out_mult        a constant factor on the mixer's result
 """
 from __future__ import annotations
 
@@ -22,7 +32,8 @@ from .spec import CacheRequest, PartSpec, TensorSpec
 @MIXERS.register("gqa_attention")
 class GQAAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (int | None),
-    position_encoding (PartSpec), and tensor names q_proj, k_proj, v_proj, o_proj."""
+    position_encoding (PartSpec), and tensor names q_proj, k_proj, v_proj, o_proj; optional qk_norm
+    ({"eps", "q_name", "k_name"}), value_from_key (bool), scale, sink (a score), out_mult."""
 
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
@@ -36,24 +47,45 @@ class GQAAttention(Mixer):
             raise ValueError(f"{self.nqh} query heads do not divide into {self.nkh} kv heads")
         pe: PartSpec = p["position_encoding"]
         self.pe = POSITION_ENCODINGS.get(pe.kind)(pe.params, prefix, runtime)
-        self.qkv = Linear(runtime, [prefix + p.get("q_proj", "self_attn.q_proj.weight"),
-                                    prefix + p.get("k_proj", "self_attn.k_proj.weight"),
-                                    prefix + p.get("v_proj", "self_attn.v_proj.weight")],
-                          [self.nqh * self.hd, self.nkh * self.hd, self.nkh * self.hd], self.hidden)
+        self.value_from_key = bool(p.get("value_from_key", False))
+        names = [prefix + p.get("q_proj", "self_attn.q_proj.weight"), prefix + p.get("k_proj", "self_attn.k_proj.weight")]
+        outs = [self.nqh * self.hd, self.nkh * self.hd]
+        if not self.value_from_key:
+            names.append(prefix + p.get("v_proj", "self_attn.v_proj.weight"))
+            outs.append(self.nkh * self.hd)
+        self.qkv = Linear(runtime, names, outs, self.hidden)
         self.o = Linear(runtime, [prefix + p.get("o_proj", "self_attn.o_proj.weight")], [self.hidden],
                         self.nqh * self.hd)
-        self.scale = 1.0 / math.sqrt(self.hd)
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
+        self.sink = float(p["sink"]) if p.get("sink") is not None else None
+        self.out_mult = float(p.get("out_mult", 1.0))
+        qn = p.get("qk_norm")
+        self.qk_norm = None
+        if qn is not None:
+            self.qk_norm = (float(qn["eps"]), prefix + qn["q_name"], prefix + qn["k_name"])
+        self.q_norm_w = self.k_norm_w = None
+        if (self.qk_norm or self.value_from_key) and not hasattr(self.pe, "norm_encode_and_store"):
+            raise ValueError(f"position encoding '{pe.kind}' cannot norm heads or store a key as the value")
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         d = dict(self.qkv.tensor_specs())
         d.update(self.o.tensor_specs())
         d.update(self.pe.tensor_specs())
+        if self.qk_norm:
+            d[self.qk_norm[1]] = TensorSpec((self.hd,), init="one_plus_normal")
+            d[self.qk_norm[2]] = TensorSpec((self.hd,), init="one_plus_normal")
         return d
 
     def load(self, tensors) -> None:
         self.qkv.load(tensors)
+        w = self.qkv.weight
+        pad = -w.shape[0] % 8            # rows of zeros, so that a row of the stacked result starts on 16 bytes
+        if pad and (self.qk_norm or self.value_from_key):     # (the plain rotation kernels take rows without padding)
+            self.qkv.weight = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)]).contiguous()
         self.o.load(tensors)
         self.pe.load(tensors)
+        if self.qk_norm:
+            self.q_norm_w, self.k_norm_w = tensors[self.qk_norm[1]], tensors[self.qk_norm[2]]
 
     def cache_request(self) -> Optional[CacheRequest]:
         kind = "window" if self.window else "full"
@@ -68,7 +100,11 @@ class GQAAttention(Mixer):
         rt = self.rt
         fused = self.pe.accepts_deferred
         qkv = self.qkv.forward(x, defer_to=ctx if fused else None, in_scale=ctx.take_row_scale(x))
-        self.pe.encode_and_store(qkv, self.nqh, self.nkh, ctx, cache)
+        if self.qk_norm or self.value_from_key:
+            self.pe.norm_encode_and_store(qkv, self.nqh, self.nkh, ctx, cache, self.q_norm_w, self.k_norm_w,
+                                          self.qk_norm[0] if self.qk_norm else 0.0, self.value_from_key)
+        else:
+            self.pe.encode_and_store(qkv, self.nqh, self.nkh, ctx, cache)
         rows = x.shape[0]
         out = rt.empty(rows, self.nqh * self.hd)
         self._attend(qkv, out, ctx, cache)
@@ -85,10 +121,13 @@ class GQAAttention(Mixer):
         plain = (self.rt.is_f32 or self.rt.attention_backend == "plain" or not K.attn_mma_supports(self.hd))
         if plain:
             K.attn_simple(qkv, out, cache.storage, cache.page_table, ctx.positions, ctx.token_seq,
-                          self.nqh, self.nkh, self.hd, cache.page_size, self.window, self.scale)
+                          self.nqh, self.nkh, self.hd, cache.page_size, self.window, self.scale, sink=self.sink,
+                          out_scale=self.out_mult)
             return
         few = ctx.max_q_len <= 8
-        if not few and self.rt.attention_backend == "auto" and K.attn_tc_supports(self.hd):
+        # the tcgen05 kernel knows neither a sink nor a factor on its result
+        if (not few and self.rt.attention_backend == "auto" and K.attn_tc_supports(self.hd) and self.sink is None
+                and self.out_mult == 1.0):
             K.attn_tc(qkv, out, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before,
                       ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, self.hd, self.window, self.scale)
             return
@@ -102,4 +141,4 @@ class GQAAttention(Mixer):
             n_splits = max(1, min(K.attn_decode_slots(self.hd) // ctas, tiles // 4, 64))
         K.attn_mma(qkv, out, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before, ctx.token_seq,
                    ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, self.hd, self.window, self.scale,
-                   n_splits=n_splits, few_tokens=few)
+                   n_splits=n_splits, few_tokens=few, sink=self.sink, out_scale=self.out_mult)

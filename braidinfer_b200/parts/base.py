@@ -132,6 +132,16 @@ class Injection(Part):
         raise NotImplementedError
 
 
+class LayerInput(Part):
+    """Something a layer adds to the stream from what it knows about each token beside the stream (a table of
+    its own, say).  The block applies it last (`LayerSpec.layer_input`)."""
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        """h: the float32 stream [rows, width], complete (no sum deferred on it); `ctx.token_ids` holds the rows'
+        tokens.  Returns the new stream (it may write into h)."""
+        raise NotImplementedError
+
+
 class Block:
     """The arrangement of a layer's parts.  `forward(h, ctx, cache, state) -> h` runs them on
     the float32 residual stream; `cache` and `state` are the mixer's (see Mixer.forward).
@@ -139,14 +149,15 @@ class Block:
     `accepts_deferred`, else call `ctx.resolve(h)` first."""
 
     def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: Optional[FeedForward],
-                 feed_forward_norm: Optional[Norm]) -> None:
+                 feed_forward_norm: Optional[Norm], layer_input: Optional[LayerInput] = None) -> None:
         self.mixer = mixer
         self.mixer_norm = mixer_norm
         self.feed_forward = feed_forward
         self.feed_forward_norm = feed_forward_norm
+        self.layer_input = layer_input
 
     def parts(self):
-        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward, self.layer_input)
                 if p is not None]
 
     def forward(self, h: torch.Tensor, ctx, cache, state) -> torch.Tensor:
@@ -186,3 +197,4 @@ BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
 INJECTIONS = Registry("injection")
+LAYER_INPUTS = Registry("layer input")

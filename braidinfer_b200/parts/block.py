@@ -3,7 +3,8 @@
 "prenorm_residual": h = h + mixer(norm(h)); h = h + feed_forward(norm(h)), the
 order of the reference's attention-plus-dense layer
 (crates/braidinfer-runtime/src/megakernel/megakernel_compile.rs:115-236).  The
-residual stream h is float32; mixers and feed-forwards add into it.
+residual stream h is float32; mixers and feed-forwards add into it.  A layer that has an input of its
+own about each token (`LayerSpec.layer_input`) applies it last: h = layer_input(h).
 """
 from __future__ import annotations
 
@@ -22,6 +23,8 @@ class PreNormResidualBlock(Block):
             h = self.feed_forward.forward(x, h, ctx)
         if ctx.row_scales:
             raise RuntimeError("a part left a row scale unapplied (see StepContext.row_scales)")
+        if self.layer_input is not None:
+            h = self.layer_input.forward(ctx.resolve(h), ctx)
         return h
 
     @staticmethod

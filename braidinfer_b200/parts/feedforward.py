@@ -1,4 +1,5 @@
-"""SwiGLU feed-forward: down( silu(gate x) * (up x) ), added to the residual
+"""Gated feed-forward: down( act(gate x) * (up x) ), added to the residual; act is silu (SwiGLU) unless the
+model names another (`activation`: "gelu_tanh" is the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))
 (reference: crates/braidinfer-runtime/src/megakernel/compile_layers.rs:373-386;
 kernels/megakernel_ops.hip:1474-1545 gate/up with silu as x / (1 + exp(-x)),
 :1559-1602 down with the residual).  Gate and up are one stacked product; on the
@@ -14,13 +15,16 @@ from .spec import TensorSpec
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
-    """params: hidden_size, intermediate_size, tensor names gate_proj, up_proj, down_proj."""
+    """params: hidden_size, intermediate_size, activation (default "silu"), tensor names gate_proj, up_proj, down_proj."""
 
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
         p = params
         self.hidden = int(p["hidden_size"])
         self.inter = int(p["intermediate_size"])
+        self.activation = p.get("activation", "silu")
+        from ..csrc.api import activation_code
+        activation_code(self.activation)                 # an unknown name fails here, not at the first step
         self.gate_up = Linear(runtime, [prefix + p.get("gate_proj", "mlp.gate_proj.weight"),
                                         prefix + p.get("up_proj", "mlp.up_proj.weight")],
                               [self.inter, self.inter], self.hidden, gate_up=True)
@@ -39,5 +43,6 @@ class SwiGLU(FeedForward):
         return self.gate_up.takes_row_scale()
 
     def forward(self, x, residual, ctx):
-        act = self.gate_up.forward(x, swiglu=True, in_scale=ctx.take_row_scale(x) if ctx is not None else None)
+        act = self.gate_up.forward(x, swiglu=True, in_scale=ctx.take_row_scale(x) if ctx is not None else None,
+                                   activation=self.activation)
         return self.down.forward(act, residual=residual, defer_to=ctx)

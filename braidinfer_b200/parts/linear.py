@@ -95,10 +95,11 @@ class Linear:
 
     def forward(self, x: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
                 residual: Optional[torch.Tensor] = None, swiglu: bool = False, defer_to=None,
-                in_scale=None) -> torch.Tensor:
+                in_scale=None, activation: str = "silu") -> torch.Tensor:
         """x [rows, in].  Plain: returns [rows, out] in `out_dtype` (default x's type).
         `residual` (float32 [rows, out]): returns residual + product, written in place.
-        `swiglu`: the weight holds gate rows then up rows; returns silu(gate) * up.
+        `swiglu`: the weight holds gate rows then up rows; returns act(gate) * up, act the
+        `activation` ("silu", or "gelu_tanh" for the tanh form of gelu).
         `defer_to` (a StepContext): when the product runs in its stream-k form, leave the
         adding-up of its partial sums to whoever reads the result next
         (`StepContext.deferred`); the returned tensor is complete only after that.
@@ -116,7 +117,7 @@ class Linear:
             x32 = torch.empty(x.shape, dtype=torch.float32, device=x.device)
             K.cast(x, x32)
             y = self.forward(x32, out_dtype=torch.float32 if residual is None else None,
-                             residual=residual, swiglu=swiglu)
+                             residual=residual, swiglu=swiglu, activation=activation)
             if residual is not None:
                 return y
             want = out_dtype or x.dtype
@@ -144,11 +145,11 @@ class Linear:
                 if not use_tc:
                     raise RuntimeError("interleaved gate/up weights need the tensor-core product; its input rows "
                                        "must be 16-byte aligned bfloat16")
-                K.gemm_tc(x, w, out, swiglu=True, stream_k=sk, in_scale=in_scale)
+                K.gemm_tc(x, w, out, swiglu=True, stream_k=sk, in_scale=in_scale, activation=activation)
             else:
                 gu = torch.empty((rows, w_rows), dtype=x.dtype, device=x.device)
                 K.gemm_simt(x, w, gu)
-                K.silu_mul(gu, out)
+                K.act_mul(gu, out, activation)
             return out
         out = torch.empty((rows, w_rows), dtype=out_dtype or x.dtype, device=x.device)
         if can_defer:

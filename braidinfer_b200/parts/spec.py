@@ -27,6 +27,9 @@ class LayerSpec:
     mixer_norm: PartSpec
     feed_forward: Optional[PartSpec] = None
     feed_forward_norm: Optional[PartSpec] = None
+    # a part (registry LAYER_INPUTS) that the block applies to the stream after its other parts: something the
+    # layer reads about each token beside the stream
+    layer_input: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

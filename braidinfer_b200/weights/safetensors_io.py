@@ -107,6 +107,11 @@ def open_model_folder(folder: str) -> Dict[str, Tuple[SafetensorsFile, str]]:
     raise FileNotFoundError(f"{folder}: neither model.safetensors nor model.safetensors.index.json")
 
 
+def tensor_shapes(folder: str) -> Dict[str, Tuple[int, ...]]:
+    """name -> shape for every tensor of a model folder (the headers are read, no data)."""
+    return {n: tuple(f.info(m)[1]) for n, (f, m) in open_model_folder(folder).items()}
+
+
 def save_file(tensors: Mapping[str, torch.Tensor], path: str, metadata: Mapping[str, str] = None) -> None:
     """Write tensors (CPU) to `path` in the order given."""
     header = {}
