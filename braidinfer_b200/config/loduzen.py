@@ -143,8 +143,6 @@ class LoduzenConfig:
         vdim = _get(m, "m.left.vdim", int, minimum=1)
         if vdim != dim:
             raise ConfigError(f"config.json: '{at}.mixer.left': the values are the keys, so vdim = {vdim} must equal dim = {dim}")
-        if dim % 2:
-            raise ConfigError(f"config.json: '{at}.mixer.left.dim' is {dim}; the rotation pairs neighbours, so it must be even")
         heads, kv = _get(m, "m.left.heads", int, minimum=1), _get(m, "m.left.kv_heads", int, minimum=1)
         if heads % kv:
             raise ConfigError(f"config.json: '{at}.mixer.left': {heads} heads do not form {kv} equal groups")

@@ -541,8 +541,8 @@ extern "C" int braid_head_norm_rope_kv(void* qk, long long row_stride, int dtype
                                        int rope_dim, int adjacent, int value_is_key, int page_size, int table_cols,
                                        int num_pages, float eps, float amp, int* error_flag, void* stream) {
     if (rows <= 0) return BRAID_OK;
-    if (nqh <= 0 || nkh <= 0 || hd <= 0 || hd > HEAD_NORM_MAX_HD || (hd & 1))
-        BRAID_REFUSE("head_norm_rope_kv: heads must be positive and head_dim=%d even and at most %d", hd, HEAD_NORM_MAX_HD);
+    if (nqh <= 0 || nkh <= 0 || hd <= 0 || hd > HEAD_NORM_MAX_HD)
+        BRAID_REFUSE("head_norm_rope_kv: heads must be positive and head_dim=%d at most %d", hd, HEAD_NORM_MAX_HD);
     if (rope_dim < 0 || rope_dim > hd || (rope_dim & 1)) BRAID_REFUSE("head_norm_rope_kv: rope_dim=%d must be even and <= head_dim=%d", rope_dim, hd);
     HeadNormRopeArgs a{qk, row_stride, q_w, k_w, inv_freq, positions, token_seq, page_table, cache, rows, nqh, nkh, hd,
                        rope_dim, adjacent, value_is_key, page_size, table_cols, num_pages, eps, amp, error_flag};
