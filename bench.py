@@ -885,6 +885,237 @@ def bidinex_kernels(z, T, B, C, timed, frac):
                      "out_of_latent_frac": round(frac(t2, 2 * rows * H * R * z["vdim"], 2 * (rows * H * (z["vdim"] + R) + H * R * z["vdim"])), 3)}
     return res
 
+# ------------------------------------------------------------------ the Loduzen decoder beside the dense one
+LODUZEN_SIZES = {
+    # width, attention heads / kv heads / head size / window, linear-attention heads / key / value size,
+    # state-space heads / value size / state / groups, feed-forward, side columns, layers (attention and state-space in turn)
+    "w2048": dict(width=2048, heads=16, kv=4, dim=128, window=1024, lheads=8, ldk=128, ldv=256, sheads=64, sp=64, sn=128, sg=8,
+                  ff=5632, side=256, layers=4, vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv=8, dim=128, window=1024, lheads=16, ldk=128, ldv=256, sheads=128, sp=64, sn=128, sg=8,
+                  ff=14336, side=256, layers=4, vocab=32768),
+    "w1024": dict(width=1024, heads=8, kv=2, dim=64, window=512, lheads=4, ldk=64, ldv=128, sheads=32, sp=64, sn=64, sg=4,
+                  ff=2816, side=128, layers=4, vocab=32768),
+}
+
+
+def loduzen_config(z):
+    left = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+            "mask": {"size": z["window"]},
+            "rot": {"base": 500000.0, "dims": z["dim"] // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    right = {"heads": z["lheads"], "dim": z["ldk"], "vdim": z["ldv"], "tau": 16.0}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0},
+           "mlp": {"kind": "dense", "ff": z["ff"]}}
+    ssm = {"type": "mamba2", "mixer": {"heads": z["sheads"], "vdim": z["sp"], "state": z["sn"], "groups": z["sg"], "conv": 4,
+                                       "norm_groups": z["sg"]}, "mlp": {"kind": "dense", "ff": z["ff"]}}
+    return {"architecture": "Loduzen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "token_side": {"dim": z["side"]}, "layers": [par if i % 2 == 0 else ssm for i in range(z["layers"])]}
+
+
+def loduzen_twin_config(z):
+    """The dense decoder of equal size: same width, layers, attention heads, head size, window, feed-forward, vocabulary."""
+    return {"architectures": ["MistralForCausalLM"], "model_type": "mistral", "torch_dtype": "bfloat16",
+            "num_hidden_layers": z["layers"], "hidden_size": z["width"], "num_attention_heads": z["heads"],
+            "num_key_value_heads": z["kv"], "head_dim": z["dim"], "intermediate_size": z["ff"], "vocab_size": z["vocab"],
+            "rope_theta": 500000.0, "rms_norm_eps": 1e-6, "sliding_window": z["window"], "tie_word_embeddings": True,
+            "max_position_embeddings": 32768}
+
+
+def run_loduzen(args):
+    """`--loduzen`: prompt and decode throughput of the Loduzen decoder at sizes like a real model's layers (random
+    weights, four layers), beside the dense decoder of equal size, and the new kernels one by one beside the dense
+    model's like kernels with their fractions of the measured peaks.  Prints one JSON line of its own; the default
+    run and its line are untouched."""
+    import torch
+    from braidinfer_b200.engine import Engine
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, reps=5, warm=2, graph=False):
+        for _ in range(warm):
+            fn()
+        run = fn
+        if graph:
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                fn()
+            run = gr.replay
+            run()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / 1e3)
+        return statistics.median(ts)
+
+    def frac(seconds, flops, nbytes):
+        return max(flops / (pk["bf16_tflops"] * 1e12), nbytes / (pk["hbm_gbs"] * 1e9)) / seconds
+
+    T, B, C = args.prompt_len, args.batch, args.context
+    sizes = [n for n in LODUZEN_SIZES if not args.sizes or n in args.sizes.split(",")]
+    out = {"metric": "loduzen_beside_dense_decoder", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic, random weights",
+           "prompt_len": T, "decode_batch": B, "decode_context": C, "peaks": pk, "l2": "flushed between timed calls", "sizes": {}}
+    with ClockSampler() as clocks:
+        for name in sizes:
+            z = LODUZEN_SIZES[name]
+            row = {}
+            for label, cfg in (("loduzen", loduzen_config(z)), ("dense", loduzen_twin_config(z))):
+                eng = Engine.from_random(cfg, 1, dtype="bfloat16", on_device=True, max_tokens=max(B * (C + 192), T + 64),
+                                         max_slots=B, verbose=False)
+                g = torch.Generator().manual_seed(0)
+                prompt = torch.randint(0, z["vocab"], (T,), generator=g).tolist()
+
+                def prefill():
+                    s = eng.open()
+                    eng.step([(s, prompt)], want="last")
+                    eng.close(s)
+                tp = timed(prefill, reps=3, warm=2)
+                prompts = [torch.randint(0, z["vocab"], (C,), generator=g).tolist() for _ in range(B)]
+                secs, ctx0, launches = device_timed_decode(eng, eng.kernels, prompts, args.steps, max(args.warmup, 3))
+                eng.check()
+                row[label] = {"prefill_tokens_per_s": round(T / tp), "prefill_ms": round(tp * 1e3, 3),
+                              "decode_tokens_per_s": round(B * args.steps / secs), "decode_ms_per_step": round(secs / args.steps * 1e3, 4),
+                              "weight_gb": round(eng.weight_bytes / 1e9, 3), "state_mb_per_sequence": round(sum(
+                                  s.shape[1] for s in eng.cache.state if s is not None) / 1e6, 3),
+                              "launches_per_decode_step": launches // args.steps}
+                del eng
+                torch.cuda.empty_cache()
+            row["kernels"] = loduzen_kernels(z, T, B, C, timed, frac)
+            out["sizes"][name] = row
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
+def loduzen_kernels(z, T, B, C, timed, frac):
+    """The new kernels alone, each beside the dense decoder's like kernel where it has one: seconds, and the fraction
+    of the measured peak that its algorithmic FLOPs or bytes (whichever bounds it) reach.  The recurrences run on the
+    ordinary float32 pipes: their `frac` is of the copy bandwidth (the bytes they must move), and `tflops` says what
+    they compute."""
+    import torch
+    from types import SimpleNamespace
+    from braidinfer_b200.cache import PAGE_SIZE
+    from braidinfer_b200.csrc.api import get_kernels
+    K = get_kernels(verbose=False)
+    dev, bf = "cuda", torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    H, nkh, hd, Wd, win = z["heads"], z["kv"], z["dim"], z["width"], z["window"]
+    res = {}
+
+    def paged(n_seqs, length):
+        blocks = -(-length // PAGE_SIZE)
+        cache = torch.randn(n_seqs * blocks, 2, nkh, PAGE_SIZE, hd, device=dev, dtype=bf) * 0.5
+        table = torch.arange(n_seqs * blocks, dtype=torch.int32, device=dev).view(n_seqs, blocks)
+        return cache, table
+
+    def steps_of(n_seqs, each, before):
+        rows = n_seqs * each
+        return SimpleNamespace(rows=rows, n_tokens=rows, n_seqs=n_seqs, q_start=i32([i * each for i in range(n_seqs)]),
+                               q_len=i32([each] * n_seqs), kv_before=i32([before] * n_seqs), slot_ids=i32(list(range(n_seqs))), max_q_len=each,
+                               token_seq=torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(each),
+                               positions=(torch.arange(each, dtype=torch.int32, device=dev) + before).repeat(n_seqs))
+
+    # ---- attention over a prompt of T tokens: the kernel with the sink beside the dense model's
+    cache, table = paged(1, T)
+    st = steps_of(1, T, 0)
+    q = torch.randn(T, (H + nkh) * hd, device=dev, dtype=bf) * 0.3
+    o = torch.empty(T, H * hd, device=dev, dtype=bf)
+    visible = sum(min(p + 1, win) for p in range(T))
+    fl = 2 * 2 * H * hd * visible
+    t = timed(lambda: K.attn_mma(q, o, cache, table, st.q_start, st.q_len, st.kv_before, st.token_seq, 1, T, H, nkh, hd, win,
+                                 hd ** -0.5, sink=0.0, out_scale=1.2), graph=True)
+    res["prompt_attention"] = {"sink_mma_ms": round(t * 1e3, 3), "sink_mma_frac": round(frac(t, fl, 0), 3)}
+    if K.attn_tc_supports(hd):
+        for label, sink in (("sink_tcgen05", 0.0), ("dense_tcgen05", None)):
+            t = timed(lambda: K.attn_tc(q, o, cache, table, st.q_start, st.q_len, st.kv_before, 1, T, H, nkh, hd, win, hd ** -0.5,
+                                        sink=sink, out_scale=1.2 if sink is not None else 1.0), graph=True)
+            res["prompt_attention"].update({label + "_ms": round(t * 1e3, 3), label + "_frac": round(frac(t, fl, 0), 3)})
+
+    # ---- attention of B decoded tokens over a context of C
+    cache, table = paged(B, C)
+    sd = steps_of(B, 1, C - 1)
+    q = torch.randn(B, (H + nkh) * hd, device=dev, dtype=bf) * 0.3
+    o = torch.empty(B, H * hd, device=dev, dtype=bf)
+    g = H // nkh
+    span = min(C, win)
+    sp = max(1, min(K.attn_decode_slots(hd) // (B * nkh * -(-g // 16)), (span // 32) // 4, 64))
+    by = B * span * 2 * nkh * hd * 2
+    for label, sink in (("sink", 0.0), ("dense", None)):
+        t = timed(lambda: K.attn_mma(q, o, cache, table, sd.q_start, sd.q_len, sd.kv_before, sd.token_seq, B, 1, H, nkh, hd, win,
+                                     hd ** -0.5, n_splits=sp, few_tokens=True, sink=sink), reps=9, graph=True)
+        res.setdefault("decode_attention", {"slices": sp}).update({label + "_mma_ms": round(t * 1e3, 4), label + "_frac": round(frac(t, 0, by), 3)})
+
+    # ---- norm of heads + rotation + cache write (one kernel) beside the dense model's rotation + cache write
+    inv = torch.rand(hd // 4, device=dev)
+    wn = torch.ones(hd, device=dev, dtype=bf)
+    for what, stp, n_seqs, length in (("prompt_prep", st, 1, T), ("decode_prep", sd, B, C)):
+        cache, table = paged(n_seqs, length)
+        rows = stp.rows
+        qk = torch.randn(rows, (H + nkh) * hd, device=dev, dtype=bf)
+        qkv = torch.randn(rows, (H + 2 * nkh) * hd, device=dev, dtype=bf)
+        t1 = timed(lambda: K.head_norm_rope_kv(qk, wn, wn, inv, stp.positions, stp.token_seq, table, cache, H, nkh, hd, hd // 2, True,
+                                               True, PAGE_SIZE, 1e-6, 1.1), reps=9, graph=True)
+        t2 = timed(lambda: K.rope_kv_write(qkv, inv, stp.positions, stp.token_seq, table, cache, H, nkh, hd, hd // 2, True, PAGE_SIZE),
+                   reps=9, graph=True)
+        by1 = rows * hd * 2 * (2 * (H + nkh) + 2 * nkh)
+        res[what] = {"norm_rope_ms": round(t1 * 1e3, 4), "norm_rope_frac": round(frac(t1, 0, by1), 3),
+                     "dense_rope_ms": round(t2 * 1e3, 4), "dense_frac": round(frac(t2, 0, by1), 3)}
+
+    # ---- the recurrences: gated linear attention (a decay per channel) and the state-space layer (a decay per head)
+    for what, stp in (("prompt", st), ("decode", sd)):
+        rows, n_seqs = stp.rows, stp.n_seqs
+        for kind, heads, groups, dk, dv in (("linear_attention", z["lheads"], z["lheads"], z["ldk"], z["ldv"]),
+                                            ("state_space", z["sheads"], z["sg"], z["sn"], z["sp"])):
+            qq = torch.randn(rows, groups * dk, device=dev, dtype=bf) * 0.1
+            kk = torch.randn(rows, groups * dk, device=dev, dtype=bf) * 0.1
+            vv = torch.randn(rows, heads * dv, device=dev, dtype=bf)
+            oo = torch.empty(rows, heads * dv, device=dev, dtype=torch.float32)
+            state = torch.zeros(n_seqs, heads * dk * dv * 4, dtype=torch.uint8, device=dev)
+            if kind == "linear_attention":
+                gate = torch.randn(rows, heads * dk, device=dev) + 3
+                bias = torch.zeros(heads * dk, device=dev, dtype=bf)
+                fn = lambda: K.linear_scan(qq, kk, vv, gate, bias, oo, state, 0, stp, heads, groups, dk, dv, "channel",
+                                           q_scale=dk ** -0.5, inv_tau=1 / 16)
+                gbytes = rows * heads * dk * 4
+            else:
+                gate = torch.randn(rows, heads, device=dev, dtype=bf)
+                bias = torch.zeros(heads, device=dev, dtype=bf)
+                al = torch.zeros(heads, device=dev, dtype=bf)
+                fn = lambda: K.linear_scan(qq, kk, vv, gate, bias, oo, state, 0, stp, heads, groups, dk, dv, "head", a_log=al, skip=al)
+                gbytes = rows * heads * 2
+            t = timed(fn, reps=5, graph=True)
+            by = rows * (2 * groups * dk * 2 + heads * dv * 2 + heads * dv * 4) + gbytes + 2 * n_seqs * heads * dk * dv * 4
+            fl = 4 * rows * heads * dk * dv
+            res[f"{what}_{kind}_scan"] = {"ms": round(t * 1e3, 4), "frac_of_bandwidth": round(by / (t * 1e9) / peaks()["hbm_gbs"], 3),
+                                          "tflops_fp32": round(fl / t / 1e12, 2), "mb": round(by / 1e6, 2)}
+        # the gated norms and the convolution that go with them
+        inner = z["sheads"] * z["sp"]
+        ch = inner + 2 * z["sg"] * z["sn"]
+        x = torch.randn(rows, ch, device=dev, dtype=bf)
+        y = torch.empty(rows, ch, device=dev, dtype=bf)
+        cw, cb = torch.randn(ch, 4, device=dev, dtype=bf), torch.zeros(ch, device=dev, dtype=bf)
+        cstate = torch.zeros(n_seqs, 3 * ch * 4, dtype=torch.uint8, device=dev)
+        t = timed(lambda: K.causal_conv(x, y, cw, cb, cstate, 0, stp), reps=9, graph=True)
+        res[f"{what}_convolution"] = {"ms": round(t * 1e3, 4), "frac": round(frac(t, 0, rows * ch * 4 + n_seqs * 3 * ch * 8), 3)}
+        yy = torch.randn(rows, inner, device=dev)
+        gt = torch.randn(rows, inner, device=dev, dtype=bf)
+        wv = torch.ones(inner, device=dev, dtype=bf)
+        ob = torch.empty(rows, inner, device=dev, dtype=bf)
+        t = timed(lambda: K.gated_norm(yy, gt, wv, ob, stp.token_seq, inner // z["sg"], True, 1e-6), reps=9, graph=True)
+        res[f"{what}_gated_norm"] = {"ms": round(t * 1e3, 4), "frac": round(frac(t, 0, rows * inner * 8), 3)}
+        hres = torch.zeros(rows, Wd, device=dev)
+        t = timed(lambda: K.rmsnorm_add(hres, hres, torch.ones(Wd, device=dev, dtype=bf), 1e-6), reps=9, graph=True)
+        res[f"{what}_side_norm_add"] = {"ms": round(t * 1e3, 4), "frac": round(frac(t, 0, rows * Wd * 12), 3)}
+        xb = torch.empty(rows, Wd, device=dev, dtype=bf)
+        t = timed(lambda: K.rmsnorm(hres, torch.ones(Wd, device=dev, dtype=bf), xb, 1e-6), reps=9, graph=True)
+        res[f"{what}_side_norm_add"].update(dense_rmsnorm_ms=round(t * 1e3, 4), dense_frac=round(frac(t, 0, rows * Wd * 6), 3))
+    return res
+
 
 def run_reference(args):
     print(json.dumps({"impl": "reference", "unavailable":
@@ -921,7 +1152,10 @@ def main() -> int:
     ap.add_argument("--bidinex", action="store_true",
                     help="the Bidinex decoder at sizes like a real model's layers beside the dense decoder of equal size, "
                          "and its kernels one by one; prints its own line (see run_bidinex)")
-    ap.add_argument("--sizes", default="", help="with --bidinex: names of BIDINEX_SIZES, with commas (default: all)")
+    ap.add_argument("--loduzen", action="store_true",
+                    help="the Loduzen decoder (attention beside linear attention, state-space layers) beside the dense "
+                         "decoder of equal size, and its kernels one by one; prints its own line (see run_loduzen)")
+    ap.add_argument("--sizes", default="", help="with --bidinex / --loduzen: names of the sizes, with commas (default: all)")
     ap.add_argument("--prompt-len", type=int, default=2048, help="with --bidinex: tokens of the timed prompt")
     ap.add_argument("--context", type=int, default=2048, help="with --bidinex: context of the timed decode steps")
     args = ap.parse_args()
@@ -932,6 +1166,8 @@ def main() -> int:
         return 2
     if args.bidinex:
         return run_bidinex(args)
+    if args.loduzen:
+        return run_loduzen(args)
     if args.sweep:
         return run_sweep(args)
     if args.prompt_timeline:

@@ -64,6 +64,7 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 PAIR_TOKEN_TILE = 256        # the token tile of the kernel that runs on pairs of SMs
+SCAN_CHUNK = 64              # tokens a chunk of a long prompt's recurrence (csrc/scan.cu); shorter steps walk in one pass
 
 
 class RowScale:
@@ -365,7 +366,7 @@ class Kernels:
             if lib.has_tc:
                 lib.braid_attn_tc.restype = c_int
                 lib.braid_attn_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong] + [c_void_p] * 4 + [c_int] * 10 + \
-                                             [c_float, c_void_p, c_void_p]
+                                             [c_float, c_int, c_float, c_float, c_void_p, c_void_p]
             lib.braid_attn_mma_decode_slots.restype = c_int
             lib.braid_attn_mma_decode_slots.argtypes = [c_int]
             lib.decode_slots = lib.braid_attn_mma_decode_slots(1)     # CTAs of the few-token kernel held at once
@@ -385,8 +386,10 @@ class Kernels:
 
     def attn_tc(self, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
                 q_start: torch.Tensor, q_len: torch.Tensor, kv_before: torch.Tensor, n_seqs: int, max_q_len: int,
-                nqh: int, nkh: int, hd: int, window: Optional[int], scale: float) -> None:
-        """bfloat16 attention of prompts over the cache on tcgen05 (head sizes 64 and 128)."""
+                nqh: int, nkh: int, hd: int, window: Optional[int], scale: float, sink: Optional[float] = None,
+                out_scale: float = 1.0) -> None:
+        """bfloat16 attention of prompts over the cache on tcgen05 (head sizes 64 and 128); `sink` and `out_scale`
+        as in `attn_simple`."""
         lib = self.attn_mma_library(hd)
         self._check_pages(cache)
         if not lib.has_tc:
@@ -396,7 +399,8 @@ class Kernels:
         rc = lib.braid_attn_tc(q.data_ptr(), out.data_ptr(), cache.data_ptr(), cache_rows, page_table.data_ptr(),
                                q_start.data_ptr(), q_len.data_ptr(), kv_before.data_ptr(), q.stride(0), out.stride(0),
                                out.shape[0], n_seqs, max_q_len, nqh, nkh, hd, page_table.shape[1], int(window or 0),
-                               float(scale), self._error_flag.data_ptr() + 12, self._stream())
+                               float(scale), int(sink is not None), float(sink or 0.0), float(out_scale),
+                               self._error_flag.data_ptr() + 12, self._stream())
         if rc != 0:
             raise KernelError(f"attn_tc: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
 
@@ -483,7 +487,9 @@ class Kernels:
                                                   c_void_p, c_longlong, c_longlong] + [c_void_p] * 4 + [c_int] * 5 + [c_void_p]
                 lib.braid_linear_scan.argtypes = [c_void_p, c_longlong] * 4 + [c_void_p] * 3 + [c_void_p, c_longlong] + \
                                                  [c_void_p, c_longlong, c_longlong] + [c_void_p] * 3 + [c_int] * 7 + \
-                                                 [c_float, c_float, c_void_p]
+                                                 [c_float, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p]
+                lib.braid_linear_scan_work_floats.argtypes = [c_int] * 7
+                lib.braid_linear_scan_work_floats.restype = c_longlong
                 lib.braid_gated_norm.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong,
                                                  c_void_p] + [c_int] * 5 + [c_float, c_float, c_void_p]
                 names = ("braid_causal_conv", "braid_linear_scan", "braid_gated_norm")
@@ -766,12 +772,15 @@ class Kernels:
     def linear_scan(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor, gate_bias: torch.Tensor,
                     out: torch.Tensor, state: torch.Tensor, state_offset: int, ctx, heads: int, groups: int, dk: int,
                     dv: int, mode: str, q_scale: float = 1.0, inv_tau: float = 1.0, a_log: Optional[torch.Tensor] = None,
-                    skip: Optional[torch.Tensor] = None) -> None:
+                    skip: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> None:
         """The recurrence S <- diag(a) S + (kappa k) v^T, o = S^T (q_scale q) + skip v, token by token along each
         sequence of the step, S float32 [heads, dk, dv] at `state_offset` bytes of each slot.  mode "channel":
         a = sigmoid(gate + gate_bias)^inv_tau per key channel (gate float32 [rows, heads * dk]); mode "head":
         dt = softplus(gate + gate_bias), a = exp(-exp(a_log) dt), kappa = dt (gate [rows, heads] in the run's
-        type).  q, k [rows, groups * dk], v [rows, heads * dv] (views are fine); out float32 [rows, heads * dv]."""
+        type).  q, k [rows, groups * dk], v [rows, heads * dv] (views are fine); out float32 [rows, heads * dv].
+        A step whose longest sequence brings at least two chunks of `chunk` tokens (default SCAN_CHUNK; 0: never)
+        walks its chunks side by side in three passes (see csrc/scan.cu); the results differ from the walk
+        token by token by rounding only."""
         lib = self.part_library("scan")
         if not (q.dtype == k.dtype == v.dtype == gate_bias.dtype) or out.dtype != torch.float32 \
                 or any(t.stride(1) != 1 for t in (q, k, v, gate, out)):
@@ -786,13 +795,17 @@ class Kernels:
                                   "of the rows' element type")
         else:
             raise KernelError(f"linear_scan: unknown decay mode {mode!r}")
-        self.launches += 1
+        chunk = SCAN_CHUNK if chunk is None else int(chunk)
+        code = 0 if mode == "channel" else 1
+        need = lib.braid_linear_scan_work_floats(ctx.n_seqs, int(ctx.max_q_len), chunk, heads, dk, dv, code)
+        work = torch.empty(need, dtype=torch.float32, device=out.device) if need > 0 else None
+        self.launches += 3 if need > 0 else 1
         self._check_lib(lib, lib.braid_linear_scan(
             q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), gate.data_ptr(), gate.stride(0),
             gate_bias.data_ptr(), _ptr(a_log), _ptr(skip), out.data_ptr(), out.stride(0),
             *self._state_args(state, state_offset), ctx.q_start.data_ptr(), ctx.q_len.data_ptr(), ctx.slot_ids.data_ptr(),
-            dtype_code(q.dtype), 0 if mode == "channel" else 1, ctx.n_seqs, heads, groups, dk, dv, float(q_scale),
-            float(inv_tau), self._stream()), "linear_scan")
+            dtype_code(q.dtype), code, ctx.n_seqs, heads, groups, dk, dv, float(q_scale),
+            float(inv_tau), int(ctx.max_q_len), chunk, _ptr(work), need, self._stream()), "linear_scan")
 
     def gated_norm(self, y: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, out: torch.Tensor, token_seq: torch.Tensor,
                    group: int, gate_first: bool, eps: float, out_scale: float = 1.0) -> None:

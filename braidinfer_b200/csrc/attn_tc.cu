@@ -158,6 +158,9 @@ struct AttnTcArgs {
     float scale_log2;
     int num_pages;
     int* error_flag;
+    int has_sink;                // the denominator counts one more term 2^sink_log2 that has no value (an attention sink)
+    float sink_log2;             // the sink's score * log2(e)
+    float out_scale;             // a constant factor on the result
 };
 
 __global__ void __launch_bounds__(FA_THREADS, 2)
@@ -419,7 +422,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             ok = __all_sync(0xffffffffu, ok);
             if (ok) {
                 tc_fence_after();
-                const float inv = 1.f / l;
+                // the sink joins the sum where the row is finished: l counts in units of 2^m; a sink far above every
+                // score makes the sum infinite and the row zero, which is the limit
+                const float inv = a.out_scale / (a.has_sink ? l + exp2f(a.sink_log2 - m) : l);
                 __nv_bfloat16* dst = a.out + (size_t)(q_start + tok0 + tl) * a.out_row_stride + (size_t)(head0 + hl) * HD;
 #pragma unroll
                 for (int h = 0; h < HD / 64; ++h) {
@@ -459,7 +464,7 @@ extern "C" int braid_attn_tc(const void* q, void* out, const void* cache, long l
                              const int* q_start, const int* q_len, const int* kv_before,
                              int q_row_stride, int out_row_stride, int rows, int n_seqs, int max_q_len,
                              int nqh, int nkh, int hd, int table_cols, int window, float scale,
-                             int* error_flag, void* stream) {
+                             int has_sink, float sink_score, float out_scale, int* error_flag, void* stream) {
     if (rows <= 0 || n_seqs <= 0) return BRAID_OK;
     if (hd != BRAID_HD) BRAID_REFUSE("attn_tc: this library was compiled for head_dim=%d, not %d", BRAID_HD, hd);
     if (nqh <= 0 || nkh <= 0 || nqh % nkh) BRAID_REFUSE("attn_tc: %d query heads do not divide into %d kv heads", nqh, nkh);
@@ -502,7 +507,7 @@ extern "C" int braid_attn_tc(const void* q, void* out, const void* cache, long l
         BRAID_REFUSE("attn_tc: the step exceeds the grid limits (%lld token tiles, %d sequences)", gx, n_seqs);
     const long long num_pages = cache_rows / (2LL * nkh * FA_PAGE);
     AttnTcArgs a{(__nv_bfloat16*)out, page_table, q_start, q_len, kv_before, out_row_stride, nqh, nkh, table_cols, window,
-                 scale * 1.4426950408889634f, (int)num_pages, error_flag};
+                 scale * 1.4426950408889634f, (int)num_pages, error_flag, has_sink, sink_score * 1.4426950408889634f, out_scale};
     braid_launch(attn_tc_kernel, dim3(nkh * hchunks, n_seqs, (unsigned)gx), dim3(FA_THREADS), FA_SMEM,
                  (cudaStream_t)stream, mq, mkv, a);
     BRAID_LAUNCH_CHECK();

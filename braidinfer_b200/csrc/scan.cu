@@ -112,14 +112,24 @@ extern "C" int braid_causal_conv(const void* x, long long x_stride, void* y, lon
 //   DECAY_HEAD (state-space duality): dt = softplus(d_t[h] + dt_bias[h]), a_t = exp(-exp(A_log[h]) dt) for every
 //       channel, kappa = dt, skip = D[h]; d in the run's type [rows, heads] (row stride gate_stride).
 // q and k: [rows, groups, dk] in the run's type (head h reads group h / (heads / groups)); v: [rows, heads, dv].
-// out: float32 [rows, heads * dv].
+// out: float32 [rows, heads * dv].  Everything is float32 arithmetic on the ordinary pipes: the recurrence, its
+// decays and its state are not to be rounded to fewer bits.
 //
-// A CTA owns (head, sequence, a tile of SCAN_DV value columns); thread (j, s) keeps dk / SCAN_KS
-// rows of column j of S in registers (rows s, s + KS, ...).  Tokens are staged SCAN_TB at a time in shared memory
-// (q, k, decay, v), so the walk itself has no block-wide barrier per token: the KS partial sums of a
-// column meet by warp shuffles.
-#define SCAN_DV 32
-#define SCAN_KS 4
+// A CTA of 128 threads owns (head, sequence, a tile of value columns); a thread keeps a tile of 8 rows x 4 columns
+// of S in registers; RG = the row groups (8 RG >= dk, a power of two up to 32) are neighbouring lanes, so that a
+// column's partial sums meet by warp shuffles.  Tokens are staged SCAN_TB at a time in shared memory (q, k, the
+// decays, v), read back 16 bytes at a time, and the walk has no block-wide barrier per token.
+//
+// Long prompts: a walk token by token is a chain as long as the prompt, on few CTAs.  For those the sequence is cut
+// into chunks of `chunk` tokens that run side by side, in three passes over the same arithmetic:
+//   pass 1  every chunk from a zero state: its own contribution U_c and the product D_c of its decays
+//   carry   per state element, chunk after chunk: S_c (the state a chunk starts from) is kept, S <- D_c S + U_c
+//   pass 3  every chunk from S_c, writing the outputs
+// The sums are the sequential ones regrouped (D (S) + U instead of a step at a time), so results differ from the
+// one-pass walk by rounding only.  Twice the arithmetic, a chain of 2 x chunk tokens, chunks x as many CTAs.
+#define SCAN_R 8
+#define SCAN_CV 4
+#define SCAN_THREADS 128
 #define SCAN_TB 8
 #define SCAN_MAX_DK 256
 #define DECAY_CHANNEL 0
@@ -138,27 +148,35 @@ struct ScanArgs {
     const int* q_start; const int* q_len; const int* slot_ids;
     int heads, groups, dk, dv;
     float q_scale, inv_tau;
+    // chunked walk (pass != 0): wbuf [seq][chunk][head][dk][dv], dbuf [seq][chunk][head]([dk])
+    float* wbuf; float* dbuf;
+    int pass, chunk, max_chunks;
 };
 
-template <typename T, int MODE, int MAX_DK>
-__global__ void __launch_bounds__(SCAN_DV * SCAN_KS)
+template <typename T, int MODE, int RG>
+__global__ void __launch_bounds__(SCAN_THREADS)
 linear_scan_kernel(ScanArgs a) {
+    constexpr int R = SCAN_R, CV = SCAN_CV, CG = SCAN_THREADS / RG, DVT = CG * CV, DKP = RG * R;
     pdl_trigger();
-    const int h = blockIdx.x, seq = blockIdx.y, j0 = blockIdx.z * SCAN_DV;
+    const int h = blockIdx.x, seq = blockIdx.y;
+    const int n_dvt = (a.dv + DVT - 1) / DVT;
+    const int dvt = blockIdx.z % n_dvt, c = blockIdx.z / n_dvt;
     const int tid = threadIdx.x;
-    const int ks = tid % SCAN_KS, jl = tid / SCAN_KS;       // the KS threads of a column are neighbours in a warp
-    const int j = j0 + jl;
+    const int rg = tid % RG, cg = tid / RG;                  // the row groups of a column group are neighbouring lanes
+    const int j0 = dvt * DVT + cg * CV;
     const int n = a.q_len[seq], r0 = a.q_start[seq];
-    if (n <= 0) return;
-    constexpr int PER = MAX_DK / SCAN_KS;                  // rows of S a thread keeps
-    const int dk = a.dk;
+    int t_begin = 0, t_end = n;
+    if (a.pass != 0) { t_begin = c * a.chunk; t_end = min(n, t_begin + a.chunk); }
+    if (t_begin >= t_end) return;
+    const int dk = a.dk, dv = a.dv;
     const int g = h / (a.heads / a.groups);
-    extern __shared__ float sm[];                           // [TB][3][dk] q, k, decay; [TB][SCAN_DV] v; [TB] kappa
-    float* sq = sm;
-    float* sk = sm + SCAN_TB * dk;
-    float* sa = sm + 2 * SCAN_TB * dk;
-    float* sv = sm + 3 * SCAN_TB * dk;
-    float* skap = sv + SCAN_TB * SCAN_DV;
+    extern __shared__ __align__(16) float sm[];
+    float* sq = sm;                                          // [TB][DKP]
+    float* sk = sq + SCAN_TB * DKP;
+    float* sv = sk + SCAN_TB * DKP;                          // [TB][DVT]
+    float* skap = sv + SCAN_TB * DVT;                        // [TB] step sizes, [TB] decays of the head
+    float* sah = skap + SCAN_TB;
+    float* sa = sah + SCAN_TB;                               // [TB][DKP] decays per channel (DECAY_CHANNEL)
     float head_a = 0.f, head_bias = 0.f, head_skip = 0.f;
     if (MODE == DECAY_HEAD) {
         head_a = -expf(to_f32(((const T*)a.a_log)[h]));
@@ -166,68 +184,156 @@ linear_scan_kernel(ScanArgs a) {
         if (a.skip) head_skip = to_f32(((const T*)a.skip)[h]);
     }
     pdl_wait();
-    float* S = (float*)(a.state + (size_t)a.slot_ids[seq] * a.state_stride + a.state_offset) + (size_t)h * dk * a.dv;
-    float s[PER];
+    const size_t per_head = (size_t)dk * dv;
+    float* S_area = (float*)(a.state + (size_t)a.slot_ids[seq] * a.state_stride + a.state_offset) + (size_t)h * per_head;
+    float* S_work = a.wbuf ? a.wbuf + ((size_t)(seq * a.max_chunks + c) * a.heads + h) * per_head : nullptr;
+    float s[R][CV];
 #pragma unroll
-    for (int e = 0; e < PER; ++e) {
-        const int i = ks + e * SCAN_KS;
-        s[e] = (i < dk && j < a.dv) ? S[(size_t)i * a.dv + j] : 0.f;
-    }
-    for (int t0 = 0; t0 < n; t0 += SCAN_TB) {
-        const int nt = min(SCAN_TB, n - t0);
-        __syncthreads();                                    // the batch before has been read
-        for (int idx = tid; idx < nt * dk; idx += blockDim.x) {
-            const int t = idx / dk, i = idx - t * dk;
-            const size_t row = (size_t)(r0 + t0 + t);
-            sq[t * dk + i] = to_f32(((const T*)a.q)[row * a.q_stride + (size_t)g * dk + i]) * a.q_scale;
-            sk[t * dk + i] = to_f32(((const T*)a.k)[row * a.k_stride + (size_t)g * dk + i]);
-            if (MODE == DECAY_CHANNEL) {
-                const float z = ((const float*)a.gate)[row * a.gate_stride + (size_t)h * dk + i] +
-                                to_f32(((const T*)a.gate_bias)[(size_t)h * dk + i]);
-                // log sigmoid(z) = -softplus(-z) = min(z, 0) - log1p(exp(-|z|))
-                const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-                sa[t * dk + i] = expf(ls * a.inv_tau);
-            }
+    for (int e = 0; e < R; ++e)
+#pragma unroll
+        for (int x = 0; x < CV; ++x) {
+            const int i = rg * R + e, j = j0 + x;
+            s[e][x] = (a.pass != 1 && i < dk && j < dv) ? (a.pass == 0 ? S_area : S_work)[(size_t)i * dv + j] : 0.f;
         }
-        for (int idx = tid; idx < nt * SCAN_DV; idx += blockDim.x) {
-            const int t = idx / SCAN_DV, jj = idx - t * SCAN_DV;
+    float dprod[R];
+#pragma unroll
+    for (int e = 0; e < R; ++e) dprod[e] = 1.f;
+    float hprod = 1.f;
+    const bool outputs = a.pass != 1;
+
+    for (int t0 = t_begin; t0 < t_end; t0 += SCAN_TB) {
+        const int nt = min(SCAN_TB, t_end - t0);
+        __syncthreads();                                    // the batch before has been read
+        for (int idx = tid; idx < nt * DKP; idx += SCAN_THREADS) {
+            const int t = idx / DKP, i = idx - t * DKP;
             const size_t row = (size_t)(r0 + t0 + t);
-            sv[idx] = (j0 + jj < a.dv) ? to_f32(((const T*)a.v)[row * a.v_stride + (size_t)h * a.dv + j0 + jj]) : 0.f;
+            float qv = 0.f, kv = 0.f, av = 0.f;
+            if (i < dk) {
+                qv = to_f32(((const T*)a.q)[row * a.q_stride + (size_t)g * dk + i]) * a.q_scale;
+                kv = to_f32(((const T*)a.k)[row * a.k_stride + (size_t)g * dk + i]);
+                if (MODE == DECAY_CHANNEL) {
+                    const float z = ((const float*)a.gate)[row * a.gate_stride + (size_t)h * dk + i] +
+                                    to_f32(((const T*)a.gate_bias)[(size_t)h * dk + i]);
+                    // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
+                    av = expf((fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * a.inv_tau);
+                }
+            }
+            sq[idx] = qv;
+            sk[idx] = kv;
+            if (MODE == DECAY_CHANNEL) sa[idx] = av;
+        }
+        for (int idx = tid; idx < nt * DVT; idx += SCAN_THREADS) {
+            const int t = idx / DVT, jj = idx - t * DVT;
+            const size_t row = (size_t)(r0 + t0 + t);
+            sv[idx] = (dvt * DVT + jj < dv) ? to_f32(((const T*)a.v)[row * a.v_stride + (size_t)h * dv + dvt * DVT + jj]) : 0.f;
         }
         if (MODE == DECAY_HEAD && tid < nt) {
             const size_t row = (size_t)(r0 + t0 + tid);
             const float x = to_f32(((const T*)a.gate)[row * a.gate_stride + h]) + head_bias;
             const float dt = x > 20.f ? x : log1pf(expf(x));           // softplus
             skap[tid] = dt;
-            sa[tid] = expf(head_a * dt);
+            sah[tid] = expf(head_a * dt);
         }
         __syncthreads();
         for (int t = 0; t < nt; ++t) {
-            const float vj = sv[t * SCAN_DV + jl];
-            const float kap = (MODE == DECAY_HEAD) ? skap[t] : 1.f;
-            const float ah = (MODE == DECAY_HEAD) ? sa[t] : 0.f;
-            const float kv = kap * vj;
-            float acc = 0.f;
+            float qv[R], kv[R], av[R], vv[CV];
+            *reinterpret_cast<float4*>(kv) = *reinterpret_cast<const float4*>(sk + t * DKP + rg * R);
+            *reinterpret_cast<float4*>(kv + 4) = *reinterpret_cast<const float4*>(sk + t * DKP + rg * R + 4);
+            *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(sv + t * DVT + cg * CV);
+            if (MODE == DECAY_CHANNEL) {
+                *reinterpret_cast<float4*>(av) = *reinterpret_cast<const float4*>(sa + t * DKP + rg * R);
+                *reinterpret_cast<float4*>(av + 4) = *reinterpret_cast<const float4*>(sa + t * DKP + rg * R + 4);
+            } else {
+                const float ah = sah[t], kap = skap[t];
+                hprod *= ah;
 #pragma unroll
-            for (int e = 0; e < PER; ++e) {
-                const int i = ks + e * SCAN_KS;
-                if (i < dk) {
-                    const float dec = (MODE == DECAY_HEAD) ? ah : sa[t * dk + i];
-                    s[e] = fmaf(dec, s[e], sk[t * dk + i] * kv);
-                    acc = fmaf(s[e], sq[t * dk + i], acc);
-                }
+                for (int e = 0; e < R; ++e) { av[e] = ah; kv[e] *= kap; }
             }
 #pragma unroll
-            for (int o = SCAN_KS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (ks == 0 && j < a.dv)
-                a.out[(size_t)(r0 + t0 + t) * a.out_stride + (size_t)h * a.dv + j] = acc + head_skip * vj;
+            for (int e = 0; e < R; ++e) {
+                dprod[e] *= av[e];
+#pragma unroll
+                for (int x = 0; x < CV; ++x) s[e][x] = fmaf(av[e], s[e][x], kv[e] * vv[x]);
+            }
+            if (outputs) {
+                *reinterpret_cast<float4*>(qv) = *reinterpret_cast<const float4*>(sq + t * DKP + rg * R);
+                *reinterpret_cast<float4*>(qv + 4) = *reinterpret_cast<const float4*>(sq + t * DKP + rg * R + 4);
+                float acc[CV];
+#pragma unroll
+                for (int x = 0; x < CV; ++x) acc[x] = 0.f;
+#pragma unroll
+                for (int e = 0; e < R; ++e)
+#pragma unroll
+                    for (int x = 0; x < CV; ++x) acc[x] = fmaf(s[e][x], qv[e], acc[x]);
+#pragma unroll
+                for (int o = RG / 2; o > 0; o >>= 1)
+#pragma unroll
+                    for (int x = 0; x < CV; ++x) acc[x] += __shfl_xor_sync(0xffffffffu, acc[x], o);
+                if (rg == 0) {
+                    float* orow = a.out + (size_t)(r0 + t0 + t) * a.out_stride + (size_t)h * dv;
+#pragma unroll
+                    for (int x = 0; x < CV; ++x)
+                        if (j0 + x < dv) orow[j0 + x] = acc[x] + head_skip * vv[x];
+                }
+            }
         }
     }
+    if (a.pass == 3) return;
+    float* dst = a.pass == 0 ? S_area : S_work;
 #pragma unroll
-    for (int e = 0; e < PER; ++e) {
-        const int i = ks + e * SCAN_KS;
-        if (i < dk && j < a.dv) S[(size_t)i * a.dv + j] = s[e];
+    for (int e = 0; e < R; ++e)
+#pragma unroll
+        for (int x = 0; x < CV; ++x) {
+            const int i = rg * R + e, j = j0 + x;
+            if (i < dk && j < dv) dst[(size_t)i * dv + j] = s[e][x];
+        }
+    if (a.pass == 1 && dvt == 0) {                           // the product of the chunk's decays, once per head
+        const size_t base = (size_t)(seq * a.max_chunks + c) * a.heads + h;
+        if (MODE == DECAY_HEAD) {
+            if (tid == 0) a.dbuf[base] = hprod;
+        } else if (cg == 0) {
+#pragma unroll
+            for (int e = 0; e < R; ++e)
+                if (rg * R + e < dk) a.dbuf[base * dk + rg * R + e] = dprod[e];
+        }
     }
+}
+
+// The carry between the chunks of a sequence: per element of the state, chunk after chunk.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+scan_carry_kernel(ScanArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t per_seq = (size_t)a.heads * a.dk * a.dv;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int seq = blockIdx.y;
+    if (idx >= per_seq) return;
+    const int n = a.q_len[seq];
+    if (n <= 0) return;
+    const int n_chunks = (n + a.chunk - 1) / a.chunk;
+    const int h = (int)(idx / ((size_t)a.dk * a.dv));
+    const int i = (int)((idx / a.dv) % a.dk);
+    float* S_area = (float*)(a.state + (size_t)a.slot_ids[seq] * a.state_stride + a.state_offset);
+    float S = S_area[idx];
+    for (int c = 0; c < n_chunks; ++c) {
+        const size_t base = (size_t)(seq * a.max_chunks + c);
+        float* w = a.wbuf + base * per_seq + idx;
+        const float u = *w;
+        const float d = MODE == DECAY_HEAD ? a.dbuf[base * a.heads + h] : a.dbuf[(base * a.heads + h) * a.dk + i];
+        *w = S;                                             // the state that chunk c starts from
+        S = fmaf(d, S, u);
+    }
+    S_area[idx] = S;
+}
+
+static int scan_rg(int dk) { return dk <= 32 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 32; }
+
+// Floats of scratch that the chunked walk of a step needs (0: the step is walked in one pass).
+extern "C" long long braid_linear_scan_work_floats(int n_seqs, int max_q_len, int chunk, int heads, int dk, int dv, int mode) {
+    if (chunk <= 0 || max_q_len < 2 * chunk) return 0;
+    const long long chunks = (max_q_len + chunk - 1) / chunk;
+    return (long long)n_seqs * chunks * heads * ((long long)dk * dv + (mode == DECAY_HEAD ? 1 : dk));
 }
 
 extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
@@ -235,33 +341,63 @@ extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* 
                                  const void* a_log, const void* skip, float* out, long long out_stride, void* state,
                                  long long state_stride, long long state_offset, const int* q_start, const int* q_len,
                                  const int* slot_ids, int dtype, int mode, int n_seqs, int heads, int groups, int dk, int dv,
-                                 float q_scale, float inv_tau, void* stream) {
+                                 float q_scale, float inv_tau, int max_q_len, int chunk, float* work, long long work_floats,
+                                 void* stream) {
     if (n_seqs <= 0) return BRAID_OK;
     if (heads <= 0 || groups <= 0 || heads % groups) BRAID_REFUSE("linear_scan: %d heads do not divide into %d groups", heads, groups);
     if (dk <= 0 || dk > SCAN_MAX_DK || dv <= 0) BRAID_REFUSE("linear_scan: key size %d must be in (0, %d], value size %d positive", dk, SCAN_MAX_DK, dv);
     if (!state || (state_offset & 3) || (state_stride & 3)) BRAID_REFUSE("linear_scan: the state area must be given, in multiples of 4 bytes");
     if (mode != DECAY_CHANNEL && mode != DECAY_HEAD) BRAID_REFUSE("linear_scan: unknown decay mode %d", mode);
     if (mode == DECAY_HEAD && !a_log) BRAID_REFUSE("linear_scan: a decay per head needs A_log");
-    if (n_seqs > 65535 || (dv + SCAN_DV - 1) / SCAN_DV > 65535) BRAID_REFUSE("linear_scan: the step exceeds the grid limits");
-    ScanArgs a{q, q_stride, k, k_stride, v, v_stride, gate, gate_stride, gate_bias, a_log, skip, out, out_stride,
-               (uint8_t*)state, state_stride, state_offset, q_start, q_len, slot_ids, heads, groups, dk, dv, q_scale, inv_tau};
-    dim3 grid(heads, n_seqs, (dv + SCAN_DV - 1) / SCAN_DV);
-    const size_t smem = (size_t)(3 * SCAN_TB * dk + SCAN_TB * SCAN_DV + SCAN_TB) * sizeof(float);
-    cudaStream_t s = (cudaStream_t)stream;
-    const dim3 block(SCAN_DV * SCAN_KS);
     if (dtype != BRAID_F32 && dtype != BRAID_BF16) BRAID_REFUSE("linear_scan: unknown dtype code %d", dtype);
-    // the kernel is compiled for key sizes up to 64, 128 and 256: a thread keeps a quarter of a column's rows in registers
-#define SCAN_LAUNCH(TT, MM)                                                                                   \
+    const int rg = scan_rg(dk);
+    const int dvt = (SCAN_THREADS / rg) * SCAN_CV;
+    const int n_dvt = (dv + dvt - 1) / dvt;
+    const long long need = braid_linear_scan_work_floats(n_seqs, max_q_len, chunk, heads, dk, dv, mode);
+    const bool chunked = need > 0 && work != nullptr;
+    if (chunked && need > work_floats) BRAID_REFUSE("linear_scan: the chunked walk needs %lld floats of scratch, it was given %lld", need, work_floats);
+    const int max_chunks = chunked ? (max_q_len + chunk - 1) / chunk : 1;
+    if (n_seqs > 65535 || (long long)n_dvt * max_chunks > 65535) BRAID_REFUSE("linear_scan: the step exceeds the grid limits");
+    ScanArgs a{q, q_stride, k, k_stride, v, v_stride, gate, gate_stride, gate_bias, a_log, skip, out, out_stride,
+               (uint8_t*)state, state_stride, state_offset, q_start, q_len, slot_ids, heads, groups, dk, dv, q_scale, inv_tau,
+               nullptr, nullptr, 0, chunk, max_chunks};
+    if (chunked) {
+        a.wbuf = work;
+        a.dbuf = work + (long long)n_seqs * max_chunks * heads * dk * dv;
+    }
+    const size_t smem = (size_t)(SCAN_TB * (2 * rg * SCAN_R + dvt + 2) + (mode == DECAY_CHANNEL ? SCAN_TB * rg * SCAN_R : 0)) * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 block(SCAN_THREADS);
+#define SCAN_LAUNCH_RG(TT, MM, GRID)                                                                          \
     do {                                                                                                      \
-        if (dk <= 64) braid_launch(linear_scan_kernel<TT, MM, 64>, grid, block, smem, s, a);                  \
-        else if (dk <= 128) braid_launch(linear_scan_kernel<TT, MM, 128>, grid, block, smem, s, a);           \
-        else braid_launch(linear_scan_kernel<TT, MM, 256>, grid, block, smem, s, a);                          \
+        if (rg == 4) braid_launch(linear_scan_kernel<TT, MM, 4>, GRID, block, smem, s, a);                    \
+        else if (rg == 8) braid_launch(linear_scan_kernel<TT, MM, 8>, GRID, block, smem, s, a);               \
+        else if (rg == 16) braid_launch(linear_scan_kernel<TT, MM, 16>, GRID, block, smem, s, a);             \
+        else braid_launch(linear_scan_kernel<TT, MM, 32>, GRID, block, smem, s, a);                           \
     } while (0)
-    if (dtype == BRAID_F32 && mode == DECAY_CHANNEL) SCAN_LAUNCH(float, DECAY_CHANNEL);
-    else if (dtype == BRAID_F32) SCAN_LAUNCH(float, DECAY_HEAD);
-    else if (mode == DECAY_CHANNEL) SCAN_LAUNCH(__nv_bfloat16, DECAY_CHANNEL);
-    else SCAN_LAUNCH(__nv_bfloat16, DECAY_HEAD);
+#define SCAN_LAUNCH(GRID)                                                                                     \
+    do {                                                                                                      \
+        if (dtype == BRAID_F32 && mode == DECAY_CHANNEL) SCAN_LAUNCH_RG(float, DECAY_CHANNEL, GRID);          \
+        else if (dtype == BRAID_F32) SCAN_LAUNCH_RG(float, DECAY_HEAD, GRID);                                 \
+        else if (mode == DECAY_CHANNEL) SCAN_LAUNCH_RG(__nv_bfloat16, DECAY_CHANNEL, GRID);                   \
+        else SCAN_LAUNCH_RG(__nv_bfloat16, DECAY_HEAD, GRID);                                                 \
+    } while (0)
+    if (!chunked) {
+        const dim3 grid(heads, n_seqs, n_dvt);
+        SCAN_LAUNCH(grid);
+        BRAID_LAUNCH_CHECK();
+    }
+    const dim3 grid(heads, n_seqs, n_dvt * max_chunks);
+    a.pass = 1;
+    SCAN_LAUNCH(grid);
+    const long long per_seq = (long long)heads * dk * dv;
+    const dim3 cgrid((unsigned)((per_seq + 255) / 256), n_seqs);
+    if (mode == DECAY_HEAD) braid_launch(scan_carry_kernel<DECAY_HEAD>, cgrid, dim3(256), 0, s, a);
+    else braid_launch(scan_carry_kernel<DECAY_CHANNEL>, cgrid, dim3(256), 0, s, a);
+    a.pass = 3;
+    SCAN_LAUNCH(grid);
 #undef SCAN_LAUNCH
+#undef SCAN_LAUNCH_RG
     BRAID_LAUNCH_CHECK();
 }
 

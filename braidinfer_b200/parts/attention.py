@@ -125,11 +125,10 @@ class GQAAttention(Mixer):
                           out_scale=self.out_mult)
             return
         few = ctx.max_q_len <= 8
-        # the tcgen05 kernel knows neither a sink nor a factor on its result
-        if (not few and self.rt.attention_backend == "auto" and K.attn_tc_supports(self.hd) and self.sink is None
-                and self.out_mult == 1.0):
+        if not few and self.rt.attention_backend == "auto" and K.attn_tc_supports(self.hd):
             K.attn_tc(qkv, out, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before,
-                      ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, self.hd, self.window, self.scale)
+                      ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, self.hd, self.window, self.scale, sink=self.sink,
+                      out_scale=self.out_mult)
             return
         n_splits = 1
         if few:

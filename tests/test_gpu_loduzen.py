@@ -190,12 +190,12 @@ def plain_attention(q, keys, values, pos, kv_len, window, scale, sink, nkh):
     return out
 
 
-@pytest.mark.parametrize("kernel", ["simple_f32", "simple_bf16", "mma_prompt", "mma_few_1", "mma_few_9"])
+@pytest.mark.parametrize("kernel", ["simple_f32", "simple_bf16", "mma_prompt", "mma_few_1", "mma_few_9", "tcgen05_prompt"])
 @pytest.mark.parametrize("window", [0, 70, 1])
 def test_attention_with_a_sink_and_a_factor_on_its_result(K, kernel, window):
     g = torch.Generator().manual_seed(window + len(kernel))
     dtype = "float32" if kernel == "simple_f32" else "bfloat16"
-    nqh, nkh, hd, page, scale, factor = 4, 2, 32, 64, 0.35, 1.3
+    nqh, nkh, hd, page, scale, factor = 4, 2, 64 if kernel == "tcgen05_prompt" else 32, 64, 0.35, 1.3
     few = kernel.startswith("mma_few")
     lengths, before = ([1, 2], [700, 130]) if few else ([150, 37], [0, 200])
     t = step_tables(lengths, before, pad=1)
@@ -233,6 +233,9 @@ def test_attention_with_a_sink_and_a_factor_on_its_result(K, kernel, window):
         if kernel.startswith("simple"):
             K.attn_simple(q, out, cache, table, t.positions, t.token_seq, nqh, nkh, hd, page, window or None, scale, sink=sink,
                           out_scale=factor)
+        elif kernel == "tcgen05_prompt":
+            K.attn_tc(q, out, cache, table, t.q_start, t.q_len, t.kv_before, 2, max(lengths), nqh, nkh, hd, window or None, scale,
+                      sink=sink, out_scale=factor)
         else:
             splits = {"mma_prompt": 1, "mma_few_1": 1, "mma_few_9": 9}[kernel]
             K.attn_mma(q, out, cache, table, t.q_start, t.q_len, t.kv_before, t.token_seq, 2, max(lengths), nqh, nkh, hd,
@@ -325,7 +328,9 @@ def test_recurrence_whole_in_portions_and_token_by_token(K, dtype, mode, heads, 
     want = [plain(*s) for s in seqs]
     offset, sbytes = 32, 32 + heads * dk * dv * 4
     tol = 1e-5                                           # the recurrence itself is float32 in both runs: same inputs, same sums
-    for cuts in ([[41, 7]], [[1, 1], [2, 2], [38, 4]], [[20, 0], [1, 7], [20, 0]]):
+    # the last walks go in chunks of 8 and of 16 tokens side by side (three passes) where a sequence brings two or more
+    for cuts, chunk in (([[41, 7]], 0), ([[1, 1], [2, 2], [38, 4]], 0), ([[20, 0], [1, 7], [20, 0]], 0), ([[41, 7]], 8),
+                        ([[3, 2], [38, 5]], 16)):
         state = torch.zeros(4, sbytes, dtype=torch.uint8, device="cuda")
         at = [0, 0]
         for cut in cuts:
@@ -336,13 +341,13 @@ def test_recurrence_whole_in_portions_and_token_by_token(K, dtype, mode, heads, 
             out = torch.zeros(t.rows, heads * dv, dtype=torch.float32, device="cuda")
             if mode == "channel":
                 K.linear_scan(q[:, :groups * dk], k, v[:, :heads * dv], gate, bias, out, state, offset, t, heads, groups, dk, dv,
-                              "channel", q_scale=dk ** -0.5, inv_tau=1 / tau)
+                              "channel", q_scale=dk ** -0.5, inv_tau=1 / tau, chunk=chunk)
             else:
                 K.linear_scan(q[:, :groups * dk], k, v[:, :heads * dv], gate[:, :heads], bias, out, state, offset, t, heads, groups,
-                              dk, dv, "head", a_log=a_log, skip=skip)
+                              dk, dv, "head", a_log=a_log, skip=skip, chunk=chunk)
             r = 0
             for i in live:
-                assert rel(out[r:r + cut[i]], want[i][0][at[i]:at[i] + cut[i]]) < tol, (cuts, cut, i)
+                assert rel(out[r:r + cut[i]], want[i][0][at[i]:at[i] + cut[i]]) < tol, (cuts, chunk, cut, i)
                 r += cut[i]
                 at[i] += cut[i]
         S = state[[3, 1], offset:].contiguous().view(torch.float32).view(2, heads, dk, dv)
