@@ -430,107 +430,140 @@ struct HeadNormRopeArgs {
 };
 
 #define HEAD_NORM_MAX_HD 512
-template <typename T>
-__global__ void __launch_bounds__(128)
+#define HEAD_NORM_WARPS 8
+template <typename T> struct Pair2;
+template <> struct Pair2<float> { using type = float2; };
+template <> struct Pair2<__nv_bfloat16> { using type = __nv_bfloat162; };
+__device__ __forceinline__ float2 pair_to_f32(float2 v) { return v; }
+__device__ __forceinline__ float2 pair_to_f32(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+template <typename P> __device__ __forceinline__ P pair_from_f32(float a, float b);
+template <> __device__ __forceinline__ float2 pair_from_f32<float2>(float a, float b) { return make_float2(a, b); }
+template <> __device__ __forceinline__ __nv_bfloat162 pair_from_f32<__nv_bfloat162>(float a, float b) { return __floats2bfloat162_rn(a, b); }
+
+// One CTA a row: sine and cosine once for the row, then a warp a head.  A lane holds whole neighbouring pairs
+// (2p, 2p+1), p = lane, lane + 32, ...; PAIRS says whether they can be moved as one word (even head size and strides).
+template <typename T, bool PAIRS>
+__global__ void __launch_bounds__(HEAD_NORM_WARPS * 32)
 head_norm_rope_kv_kernel(HeadNormRopeArgs a) {
     pdl_trigger();
     pdl_wait();
+    using P2 = typename Pair2<T>::type;
+    __shared__ float cs[HEAD_NORM_MAX_HD / 2], sn[HEAD_NORM_MAX_HD / 2];
+    __shared__ float stage[HEAD_NORM_WARPS][HEAD_NORM_MAX_HD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int heads = a.nqh + (a.value_is_key ? a.nkh : 2 * a.nkh);
-    const long long item = (long long)blockIdx.x * 4 + warp;
-    if (item >= (long long)a.rows * heads) return;
-    const int row = (int)(item / heads), head = (int)(item - (long long)row * heads);
+    const int row = blockIdx.x;
     const int seq = a.token_seq[row];
     if (seq < 0) return;
     const int pos = a.positions[row];
-    const bool is_q = head < a.nqh, is_k = !is_q && head < a.nqh + a.nkh;
-    T* src = (T*)a.qk + (size_t)row * a.row_stride + (size_t)head * a.hd;
-    T* kdst = nullptr;
-    T* vdst = nullptr;
-    if (!is_q && a.cache) {
-        const int kvh = is_k ? head - a.nqh : head - a.nqh - a.nkh;
-        const int block = pos / a.page_size, off = pos - block * a.page_size;
-        int page = (block < a.table_cols) ? a.page_table[(size_t)seq * a.table_cols + block] : -1;
-        if (page < 0 || page >= a.num_pages) {
-            if (lane == 0) atomicExch(a.error_flag, 1);
-        } else {
-            T* kplane = (T*)a.cache + ((((size_t)page * 2) * a.nkh + kvh) * a.page_size + off) * a.hd;
-            T* vplane = kplane + (size_t)a.nkh * a.page_size * a.hd;
-            if (is_k) { kdst = kplane; if (a.value_is_key) vdst = vplane; }
-            else vdst = vplane;
-        }
-    }
-    constexpr int PER = HEAD_NORM_MAX_HD / 32;
-    float x[PER];
-    // element e of this lane is head element 2 * (lane + 32 * (e / 2)) + (e & 1): a lane holds whole adjacent pairs
-    float ss = 0.f;
-#pragma unroll
-    for (int e = 0; e < PER; ++e) {
-        const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
-        x[e] = i < a.hd ? to_f32(src[i]) : 0.f;
-        ss = fmaf(x[e], x[e], ss);
-    }
-    if (vdst) {
-#pragma unroll
-        for (int e = 0; e < PER; ++e) {
-            const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
-            if (i < a.hd) vdst[i] = from_f32<T>(x[e]);
-        }
-    }
-    if (!is_q && !is_k) return;
-    const void* wv = is_q ? a.q_w : a.k_w;
-    if (wv) {
-        ss = warp_sum(ss);
-        const float r = 1.f / sqrtf(ss / (float)a.hd + a.eps);
-#pragma unroll
-        for (int e = 0; e < PER; ++e) {
-            const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
-            if (i < a.hd) x[e] = x[e] * r * to_f32(((const T*)wv)[i]);
-        }
-    }
     const int half = a.rope_dim / 2;
-    if (a.adjacent) {
-#pragma unroll
-        for (int e = 0; e < PER; e += 2) {
-            const int p = lane + 32 * (e >> 1);
-            if (p < half) {
-                float sn, cs;
-                sincosf((float)pos * a.inv_freq[p], &sn, &cs);
-                sn *= a.amp; cs *= a.amp;
-                const float u = x[e], v = x[e + 1];
-                x[e] = u * cs - v * sn;
-                x[e + 1] = v * cs + u * sn;
-            }
-        }
-    } else if (half > 0) {
-        // pairs (p, p + half) lie in different lanes: through shared memory
-        __shared__ float stage[4][HEAD_NORM_MAX_HD];
-        float* st = stage[warp];
-#pragma unroll
-        for (int e = 0; e < PER; ++e) {
-            const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
-            if (i < a.hd) st[i] = x[e];
-        }
-        __syncwarp();
-#pragma unroll
-        for (int e = 0; e < PER; ++e) {
-            const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
-            if (i < a.rope_dim) {
-                const int p = i < half ? i : i - half;
-                float sn, cs;
-                sincosf((float)pos * a.inv_freq[p], &sn, &cs);
-                sn *= a.amp; cs *= a.amp;
-                x[e] = i < half ? st[i] * cs - st[i + half] * sn : st[i] * cs + st[i - half] * sn;
-            }
+    for (int p = threadIdx.x; p < half; p += blockDim.x) {
+        float s_, c_;
+        sincosf((float)pos * a.inv_freq[p], &s_, &c_);
+        cs[p] = c_ * a.amp;
+        sn[p] = s_ * a.amp;
+    }
+    __syncthreads();
+    T* kbase = nullptr;                                    // the row's place in the key plane, kv head 0
+    if (a.cache) {
+        const int block = pos / a.page_size, off = pos - block * a.page_size;
+        const int page = (block < a.table_cols) ? a.page_table[(size_t)seq * a.table_cols + block] : -1;
+        if (page < 0 || page >= a.num_pages) {
+            if (threadIdx.x == 0) atomicExch(a.error_flag, 1);
+        } else {
+            kbase = (T*)a.cache + (((size_t)page * 2) * a.nkh * a.page_size + off) * a.hd;
         }
     }
+    const size_t plane = (size_t)a.nkh * a.page_size * a.hd, head_step = (size_t)a.page_size * a.hd;
+    const int heads = a.nqh + (a.value_is_key ? a.nkh : 2 * a.nkh);
+    constexpr int NP = HEAD_NORM_MAX_HD / 64;             // pairs a lane
+    for (int head = warp; head < heads; head += HEAD_NORM_WARPS) {
+        const bool is_q = head < a.nqh, is_k = !is_q && head < a.nqh + a.nkh;
+        T* src = (T*)a.qk + (size_t)row * a.row_stride + (size_t)head * a.hd;
+        T* kdst = nullptr;
+        T* vdst = nullptr;
+        if (!is_q && kbase) {
+            const int kvh = is_k ? head - a.nqh : head - a.nqh - a.nkh;
+            if (is_k) { kdst = kbase + kvh * head_step; if (a.value_is_key) vdst = kdst + plane; }
+            else vdst = kbase + plane + kvh * head_step;
+        }
+        float x0[NP], x1[NP];
+        float ss = 0.f;
 #pragma unroll
-    for (int e = 0; e < PER; ++e) {
-        const int i = 2 * (lane + 32 * (e >> 1)) + (e & 1);
-        if (i < a.hd) {
-            const T y = from_f32<T>(x[e]);
-            src[i] = y;
-            if (kdst) kdst[i] = y;
+        for (int e = 0; e < NP; ++e) {
+            const int i = 2 * (lane + 32 * e);
+            x0[e] = x1[e] = 0.f;
+            if (PAIRS) {
+                if (i < a.hd) {
+                    const P2 raw = *reinterpret_cast<const P2*>(src + i);
+                    if (vdst) *reinterpret_cast<P2*>(vdst + i) = raw;
+                    const float2 f = pair_to_f32(raw);
+                    x0[e] = f.x; x1[e] = f.y;
+                }
+            } else {
+                if (i < a.hd) { const T r0 = src[i]; if (vdst) vdst[i] = r0; x0[e] = to_f32(r0); }
+                if (i + 1 < a.hd) { const T r1 = src[i + 1]; if (vdst) vdst[i + 1] = r1; x1[e] = to_f32(r1); }
+            }
+            ss = fmaf(x0[e], x0[e], fmaf(x1[e], x1[e], ss));
+        }
+        if (!is_q && !is_k) continue;
+        const void* wv = is_q ? a.q_w : a.k_w;
+        if (wv) {
+            ss = warp_sum(ss);
+            const float r = 1.f / sqrtf(ss / (float)a.hd + a.eps);
+#pragma unroll
+            for (int e = 0; e < NP; ++e) {
+                const int i = 2 * (lane + 32 * e);
+                if (i < a.hd) x0[e] = x0[e] * r * to_f32(((const T*)wv)[i]);
+                if (i + 1 < a.hd) x1[e] = x1[e] * r * to_f32(((const T*)wv)[i + 1]);
+            }
+        }
+        if (a.adjacent) {
+#pragma unroll
+            for (int e = 0; e < NP; ++e) {
+                const int p = lane + 32 * e;
+                if (p < half) {
+                    const float u = x0[e], v = x1[e];
+                    x0[e] = u * cs[p] - v * sn[p];
+                    x1[e] = v * cs[p] + u * sn[p];
+                }
+            }
+        } else if (half > 0) {
+            // pairs (p, p + half) lie in different lanes: through shared memory
+            float* st = stage[warp];
+#pragma unroll
+            for (int e = 0; e < NP; ++e) {
+                const int i = 2 * (lane + 32 * e);
+                if (i < a.hd) st[i] = x0[e];
+                if (i + 1 < a.hd) st[i + 1] = x1[e];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int e = 0; e < NP; ++e) {
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    const int i = 2 * (lane + 32 * e) + b;
+                    if (i < a.rope_dim) {
+                        const int p = i < half ? i : i - half;
+                        const float y = i < half ? st[i] * cs[p] - st[i + half] * sn[p] : st[i] * cs[p] + st[i - half] * sn[p];
+                        if (b) x1[e] = y; else x0[e] = y;
+                    }
+                }
+            }
+            __syncwarp();
+        }
+#pragma unroll
+        for (int e = 0; e < NP; ++e) {
+            const int i = 2 * (lane + 32 * e);
+            if (PAIRS) {
+                if (i < a.hd) {
+                    const P2 y = pair_from_f32<P2>(x0[e], x1[e]);
+                    *reinterpret_cast<P2*>(src + i) = y;
+                    if (kdst) *reinterpret_cast<P2*>(kdst + i) = y;
+                }
+            } else {
+                if (i < a.hd) { const T y = from_f32<T>(x0[e]); src[i] = y; if (kdst) kdst[i] = y; }
+                if (i + 1 < a.hd) { const T y = from_f32<T>(x1[e]); src[i + 1] = y; if (kdst) kdst[i + 1] = y; }
+            }
         }
     }
 }
@@ -546,13 +579,18 @@ extern "C" int braid_head_norm_rope_kv(void* qk, long long row_stride, int dtype
     if (rope_dim < 0 || rope_dim > hd || (rope_dim & 1)) BRAID_REFUSE("head_norm_rope_kv: rope_dim=%d must be even and <= head_dim=%d", rope_dim, hd);
     HeadNormRopeArgs a{qk, row_stride, q_w, k_w, inv_freq, positions, token_seq, page_table, cache, rows, nqh, nkh, hd,
                        rope_dim, adjacent, value_is_key, page_size, table_cols, num_pages, eps, amp, error_flag};
-    const long long items = (long long)rows * (nqh + (value_is_key ? nkh : 2 * nkh));
-    const long long blocks = (items + 3) / 4;
-    if (blocks > 0x7fffffffLL) BRAID_REFUSE("head_norm_rope_kv: %lld (row, head) pairs exceed one launch", items);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == BRAID_F32) braid_launch(head_norm_rope_kv_kernel<float>, dim3((int)blocks), dim3(128), 0, s, a);
-    else if (dtype == BRAID_BF16) braid_launch(head_norm_rope_kv_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(128), 0, s, a);
-    else BRAID_REFUSE("head_norm_rope_kv: unknown dtype code %d", dtype);
+    const int esize = dtype == BRAID_F32 ? 4 : 2;
+    // pairs move as one word where every head starts on a pair's boundary, in the rows and in the cache
+    const bool pairs = (hd % 2 == 0) && (row_stride % 2 == 0) && (((uintptr_t)qk | (uintptr_t)cache) % (2 * esize) == 0);
+    const dim3 grid(rows), block(HEAD_NORM_WARPS * 32);
+    if (dtype == BRAID_F32) {
+        if (pairs) braid_launch(head_norm_rope_kv_kernel<float, true>, grid, block, 0, s, a);
+        else braid_launch(head_norm_rope_kv_kernel<float, false>, grid, block, 0, s, a);
+    } else if (dtype == BRAID_BF16) {
+        if (pairs) braid_launch(head_norm_rope_kv_kernel<__nv_bfloat16, true>, grid, block, 0, s, a);
+        else braid_launch(head_norm_rope_kv_kernel<__nv_bfloat16, false>, grid, block, 0, s, a);
+    } else BRAID_REFUSE("head_norm_rope_kv: unknown dtype code %d", dtype);
     BRAID_LAUNCH_CHECK();
 }
 

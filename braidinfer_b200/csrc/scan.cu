@@ -115,10 +115,12 @@ extern "C" int braid_causal_conv(const void* x, long long x_stride, void* y, lon
 // out: float32 [rows, heads * dv].  Everything is float32 arithmetic on the ordinary pipes: the recurrence, its
 // decays and its state are not to be rounded to fewer bits.
 //
-// A CTA of 128 threads owns (head, sequence, a tile of value columns); a thread keeps a tile of 8 rows x 4 columns
-// of S in registers; RG = the row groups (8 RG >= dk, a power of two up to 32) are neighbouring lanes, so that a
-// column's partial sums meet by warp shuffles.  Tokens are staged SCAN_TB at a time in shared memory (q, k, the
-// decays, v), read back 16 bytes at a time, and the walk has no block-wide barrier per token.
+// A CTA of 128 threads owns (head, sequence, a tile of value columns); a thread keeps a tile of R rows x 4 columns
+// of S in registers (R = 8, or 16 for key sizes above 128); the RG row groups (R RG >= dk, RG a power of two up to
+// 16) of a column group lie in one warp, so that a column's partial sums meet by warp shuffles, and two
+// neighbouring lanes hold neighbouring column groups, so that a pair's loads and stores of S fill whole 32-byte
+// sectors.  Tokens are staged SCAN_TB at a time in shared memory (q, k, the decays, v), read back 16 bytes at a
+// time, and the walk has no block-wide barrier per token.
 //
 // Long prompts: a walk token by token is a chain as long as the prompt, on few CTAs.  For those the sequence is cut
 // into chunks of `chunk` tokens that run side by side, in three passes over the same arithmetic:
@@ -127,7 +129,6 @@ extern "C" int braid_causal_conv(const void* x, long long x_stride, void* y, lon
 //   pass 3  every chunk from S_c, writing the outputs
 // The sums are the sequential ones regrouped (D (S) + U instead of a step at a time), so results differ from the
 // one-pass walk by rounding only.  Twice the arithmetic, a chain of 2 x chunk tokens, chunks x as many CTAs.
-#define SCAN_R 8
 #define SCAN_CV 4
 #define SCAN_THREADS 128
 #define SCAN_TB 8
@@ -153,16 +154,18 @@ struct ScanArgs {
     int pass, chunk, max_chunks;
 };
 
-template <typename T, int MODE, int RG>
+template <typename T, int MODE, int RG, int R>
 __global__ void __launch_bounds__(SCAN_THREADS)
 linear_scan_kernel(ScanArgs a) {
-    constexpr int R = SCAN_R, CV = SCAN_CV, CG = SCAN_THREADS / RG, DVT = CG * CV, DKP = RG * R;
+    constexpr int CV = SCAN_CV, CG = SCAN_THREADS / RG, DVT = CG * CV, DKP = RG * R;
+    static_assert(RG >= 2 && RG <= 16 && (R == 8 || R == 16), "two column groups and RG row groups share a warp");
     pdl_trigger();
     const int h = blockIdx.x, seq = blockIdx.y;
     const int n_dvt = (a.dv + DVT - 1) / DVT;
     const int dvt = blockIdx.z % n_dvt, c = blockIdx.z / n_dvt;
     const int tid = threadIdx.x;
-    const int rg = tid % RG, cg = tid / RG;                  // the row groups of a column group are neighbouring lanes
+    // lane bit 0: the lower bit of the column group; the next bits: the row group; what is left: the column group's rest
+    const int rg = (tid >> 1) % RG, cg = (tid & 1) | ((tid / (2 * RG)) << 1);
     const int j0 = dvt * DVT + cg * CV;
     const int n = a.q_len[seq], r0 = a.q_start[seq];
     int t_begin = 0, t_end = n;
@@ -237,12 +240,14 @@ linear_scan_kernel(ScanArgs a) {
         __syncthreads();
         for (int t = 0; t < nt; ++t) {
             float qv[R], kv[R], av[R], vv[CV];
-            *reinterpret_cast<float4*>(kv) = *reinterpret_cast<const float4*>(sk + t * DKP + rg * R);
-            *reinterpret_cast<float4*>(kv + 4) = *reinterpret_cast<const float4*>(sk + t * DKP + rg * R + 4);
+#pragma unroll
+            for (int e = 0; e < R; e += 4)
+                *reinterpret_cast<float4*>(kv + e) = *reinterpret_cast<const float4*>(sk + t * DKP + rg * R + e);
             *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(sv + t * DVT + cg * CV);
             if (MODE == DECAY_CHANNEL) {
-                *reinterpret_cast<float4*>(av) = *reinterpret_cast<const float4*>(sa + t * DKP + rg * R);
-                *reinterpret_cast<float4*>(av + 4) = *reinterpret_cast<const float4*>(sa + t * DKP + rg * R + 4);
+#pragma unroll
+                for (int e = 0; e < R; e += 4)
+                    *reinterpret_cast<float4*>(av + e) = *reinterpret_cast<const float4*>(sa + t * DKP + rg * R + e);
             } else {
                 const float ah = sah[t], kap = skap[t];
                 hprod *= ah;
@@ -256,8 +261,9 @@ linear_scan_kernel(ScanArgs a) {
                 for (int x = 0; x < CV; ++x) s[e][x] = fmaf(av[e], s[e][x], kv[e] * vv[x]);
             }
             if (outputs) {
-                *reinterpret_cast<float4*>(qv) = *reinterpret_cast<const float4*>(sq + t * DKP + rg * R);
-                *reinterpret_cast<float4*>(qv + 4) = *reinterpret_cast<const float4*>(sq + t * DKP + rg * R + 4);
+#pragma unroll
+                for (int e = 0; e < R; e += 4)
+                    *reinterpret_cast<float4*>(qv + e) = *reinterpret_cast<const float4*>(sq + t * DKP + rg * R + e);
                 float acc[CV];
 #pragma unroll
                 for (int x = 0; x < CV; ++x) acc[x] = 0.f;
@@ -266,7 +272,7 @@ linear_scan_kernel(ScanArgs a) {
 #pragma unroll
                     for (int x = 0; x < CV; ++x) acc[x] = fmaf(s[e][x], qv[e], acc[x]);
 #pragma unroll
-                for (int o = RG / 2; o > 0; o >>= 1)
+                for (int o = RG; o >= 2; o >>= 1)          // the row groups are lane bits 1 ...
 #pragma unroll
                     for (int x = 0; x < CV; ++x) acc[x] += __shfl_xor_sync(0xffffffffu, acc[x], o);
                 if (rg == 0) {
@@ -327,7 +333,8 @@ scan_carry_kernel(ScanArgs a) {
     S_area[idx] = S;
 }
 
-static int scan_rg(int dk) { return dk <= 32 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 32; }
+static int scan_rg(int dk) { return dk <= 32 ? 4 : dk <= 64 ? 8 : 16; }
+static int scan_rows(int dk) { return dk <= 128 ? 8 : 16; }
 
 // Floats of scratch that the chunked walk of a step needs (0: the step is walked in one pass).
 extern "C" long long braid_linear_scan_work_floats(int n_seqs, int max_q_len, int chunk, int heads, int dk, int dv, int mode) {
@@ -350,7 +357,7 @@ extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* 
     if (mode != DECAY_CHANNEL && mode != DECAY_HEAD) BRAID_REFUSE("linear_scan: unknown decay mode %d", mode);
     if (mode == DECAY_HEAD && !a_log) BRAID_REFUSE("linear_scan: a decay per head needs A_log");
     if (dtype != BRAID_F32 && dtype != BRAID_BF16) BRAID_REFUSE("linear_scan: unknown dtype code %d", dtype);
-    const int rg = scan_rg(dk);
+    const int rg = scan_rg(dk), rr = scan_rows(dk);
     const int dvt = (SCAN_THREADS / rg) * SCAN_CV;
     const int n_dvt = (dv + dvt - 1) / dvt;
     const long long need = braid_linear_scan_work_floats(n_seqs, max_q_len, chunk, heads, dk, dv, mode);
@@ -365,15 +372,15 @@ extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* 
         a.wbuf = work;
         a.dbuf = work + (long long)n_seqs * max_chunks * heads * dk * dv;
     }
-    const size_t smem = (size_t)(SCAN_TB * (2 * rg * SCAN_R + dvt + 2) + (mode == DECAY_CHANNEL ? SCAN_TB * rg * SCAN_R : 0)) * sizeof(float);
+    const size_t smem = (size_t)(SCAN_TB * (2 * rg * rr + dvt + 2) + (mode == DECAY_CHANNEL ? SCAN_TB * rg * rr : 0)) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 block(SCAN_THREADS);
 #define SCAN_LAUNCH_RG(TT, MM, GRID)                                                                          \
     do {                                                                                                      \
-        if (rg == 4) braid_launch(linear_scan_kernel<TT, MM, 4>, GRID, block, smem, s, a);                    \
-        else if (rg == 8) braid_launch(linear_scan_kernel<TT, MM, 8>, GRID, block, smem, s, a);               \
-        else if (rg == 16) braid_launch(linear_scan_kernel<TT, MM, 16>, GRID, block, smem, s, a);             \
-        else braid_launch(linear_scan_kernel<TT, MM, 32>, GRID, block, smem, s, a);                           \
+        if (rg == 4) braid_launch(linear_scan_kernel<TT, MM, 4, 8>, GRID, block, smem, s, a);                 \
+        else if (rg == 8) braid_launch(linear_scan_kernel<TT, MM, 8, 8>, GRID, block, smem, s, a);            \
+        else if (rr == 8) braid_launch(linear_scan_kernel<TT, MM, 16, 8>, GRID, block, smem, s, a);           \
+        else braid_launch(linear_scan_kernel<TT, MM, 16, 16>, GRID, block, smem, s, a);                       \
     } while (0)
 #define SCAN_LAUNCH(GRID)                                                                                     \
     do {                                                                                                      \
