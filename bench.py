@@ -1077,10 +1077,10 @@ def loduzen_kernels(z, T, B, C, timed, frac):
             oo = torch.empty(rows, heads * dv, device=dev, dtype=torch.float32)
             state = torch.zeros(n_seqs, heads * dk * dv * 4, dtype=torch.uint8, device=dev)
             if kind == "linear_attention":
-                gate = torch.randn(rows, heads * dk, device=dev) + 3
+                gate = torch.rand(rows, heads * dk, device=dev) * 0.1 + 0.9     # the decays themselves in a long step
                 bias = torch.zeros(heads * dk, device=dev, dtype=bf)
                 fn = lambda: K.linear_scan(qq, kk, vv, gate, bias, oo, state, 0, stp, heads, groups, dk, dv, "channel",
-                                           q_scale=dk ** -0.5, inv_tau=1 / 16)
+                                           q_scale=dk ** -0.5, inv_tau=1 / 16, gate_is_decay=rows > 64)
                 gbytes = rows * heads * dk * 4
             else:
                 gate = torch.randn(rows, heads, device=dev, dtype=bf)

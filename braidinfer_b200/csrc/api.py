@@ -487,12 +487,13 @@ class Kernels:
                                                   c_void_p, c_longlong, c_longlong] + [c_void_p] * 4 + [c_int] * 5 + [c_void_p]
                 lib.braid_linear_scan.argtypes = [c_void_p, c_longlong] * 4 + [c_void_p] * 3 + [c_void_p, c_longlong] + \
                                                  [c_void_p, c_longlong, c_longlong] + [c_void_p] * 3 + [c_int] * 7 + \
-                                                 [c_float, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p]
+                                                 [c_float, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p]
+                lib.braid_scan_decay.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
                 lib.braid_linear_scan_work_floats.argtypes = [c_int] * 7
                 lib.braid_linear_scan_work_floats.restype = c_longlong
                 lib.braid_gated_norm.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong,
                                                  c_void_p] + [c_int] * 5 + [c_float, c_float, c_void_p]
-                names = ("braid_causal_conv", "braid_linear_scan", "braid_gated_norm")
+                names = ("braid_causal_conv", "braid_linear_scan", "braid_gated_norm", "braid_scan_decay")
             elif name == "moe":
                 lib.braid_moe_route.argtypes = [c_void_p] * 3 + [c_int] * 5 + [c_float, c_void_p]
                 lib.braid_moe_plan.argtypes = [c_void_p] * 6 + [c_int] * 5 + [c_void_p]
@@ -772,12 +773,13 @@ class Kernels:
     def linear_scan(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor, gate_bias: torch.Tensor,
                     out: torch.Tensor, state: torch.Tensor, state_offset: int, ctx, heads: int, groups: int, dk: int,
                     dv: int, mode: str, q_scale: float = 1.0, inv_tau: float = 1.0, a_log: Optional[torch.Tensor] = None,
-                    skip: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> None:
+                    skip: Optional[torch.Tensor] = None, chunk: Optional[int] = None, gate_is_decay: bool = False) -> None:
         """The recurrence S <- diag(a) S + (kappa k) v^T, o = S^T (q_scale q) + skip v, token by token along each
         sequence of the step, S float32 [heads, dk, dv] at `state_offset` bytes of each slot.  mode "channel":
         a = sigmoid(gate + gate_bias)^inv_tau per key channel (gate float32 [rows, heads * dk]); mode "head":
         dt = softplus(gate + gate_bias), a = exp(-exp(a_log) dt), kappa = dt (gate [rows, heads] in the run's
         type).  q, k [rows, groups * dk], v [rows, heads * dv] (views are fine); out float32 [rows, heads * dv].
+        `gate_is_decay` (mode "channel"): `gate` holds the decays themselves, as `scan_decay` left them.
         A step whose longest sequence brings at least two chunks of `chunk` tokens (default SCAN_CHUNK; 0: never)
         walks its chunks side by side in three passes (see csrc/scan.cu); the results differ from the walk
         token by token by rounding only."""
@@ -805,7 +807,17 @@ class Kernels:
             gate_bias.data_ptr(), _ptr(a_log), _ptr(skip), out.data_ptr(), out.stride(0),
             *self._state_args(state, state_offset), ctx.q_start.data_ptr(), ctx.q_len.data_ptr(), ctx.slot_ids.data_ptr(),
             dtype_code(q.dtype), code, ctx.n_seqs, heads, groups, dk, dv, float(q_scale),
-            float(inv_tau), int(ctx.max_q_len), chunk, _ptr(work), need, self._stream()), "linear_scan")
+            float(inv_tau), int(ctx.max_q_len), chunk, _ptr(work), need, int(gate_is_decay), self._stream()), "linear_scan")
+
+    def scan_decay(self, z: torch.Tensor, bias: torch.Tensor, inv_tau: float) -> None:
+        """z <- sigmoid(z + bias)^inv_tau in place (z float32 [rows, n]): the decays of a recurrence from their logits,
+        once for a long step instead of in every CTA of the recurrence."""
+        lib = self.part_library("scan")
+        if z.dtype != torch.float32 or z.stride(1) != 1 or bias.numel() != z.shape[1]:
+            raise KernelError("scan_decay: z float32 [rows, n] with contiguous rows, bias of n numbers")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_scan_decay(z.data_ptr(), z.stride(0), bias.data_ptr(), dtype_code(bias.dtype), z.shape[0],
+                                                  z.shape[1], float(inv_tau), self._stream()), "scan_decay")
 
     def gated_norm(self, y: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, out: torch.Tensor, token_seq: torch.Tensor,
                    group: int, gate_first: bool, eps: float, out_scale: float = 1.0) -> None:

@@ -430,7 +430,7 @@ struct HeadNormRopeArgs {
 };
 
 #define HEAD_NORM_MAX_HD 512
-#define HEAD_NORM_WARPS 8
+#define HEAD_NORM_WARPS 4
 template <typename T> struct Pair2;
 template <> struct Pair2<float> { using type = float2; };
 template <> struct Pair2<__nv_bfloat16> { using type = __nv_bfloat162; };
@@ -440,43 +440,40 @@ template <typename P> __device__ __forceinline__ P pair_from_f32(float a, float 
 template <> __device__ __forceinline__ float2 pair_from_f32<float2>(float a, float b) { return make_float2(a, b); }
 template <> __device__ __forceinline__ __nv_bfloat162 pair_from_f32<__nv_bfloat162>(float a, float b) { return __floats2bfloat162_rn(a, b); }
 
-// One CTA a row: sine and cosine once for the row, then a warp a head.  A lane holds whole neighbouring pairs
+// A warp a (row, head); the warps of a CTA take neighbouring heads of one row.  A lane holds whole neighbouring pairs
 // (2p, 2p+1), p = lane, lane + 32, ...; PAIRS says whether they can be moved as one word (even head size and strides).
+// (One CTA a row with sine and cosine shared by its heads was measured too: a warp then walks several heads one
+// after the other, each a chain of load, sum, rotation and store, and the kernel took 1.5 times as long.)
 template <typename T, bool PAIRS>
 __global__ void __launch_bounds__(HEAD_NORM_WARPS * 32)
 head_norm_rope_kv_kernel(HeadNormRopeArgs a) {
     pdl_trigger();
     pdl_wait();
     using P2 = typename Pair2<T>::type;
-    __shared__ float cs[HEAD_NORM_MAX_HD / 2], sn[HEAD_NORM_MAX_HD / 2];
     __shared__ float stage[HEAD_NORM_WARPS][HEAD_NORM_MAX_HD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x;
+    const int heads = a.nqh + (a.value_is_key ? a.nkh : 2 * a.nkh);
+    const int per_row = (heads + HEAD_NORM_WARPS - 1) / HEAD_NORM_WARPS;          // CTAs a row
+    const int row = blockIdx.x / per_row;
+    const int head = (blockIdx.x - row * per_row) * HEAD_NORM_WARPS + warp;
+    if (head >= heads) return;
     const int seq = a.token_seq[row];
     if (seq < 0) return;
     const int pos = a.positions[row];
     const int half = a.rope_dim / 2;
-    for (int p = threadIdx.x; p < half; p += blockDim.x) {
-        float s_, c_;
-        sincosf((float)pos * a.inv_freq[p], &s_, &c_);
-        cs[p] = c_ * a.amp;
-        sn[p] = s_ * a.amp;
-    }
-    __syncthreads();
     T* kbase = nullptr;                                    // the row's place in the key plane, kv head 0
     if (a.cache) {
         const int block = pos / a.page_size, off = pos - block * a.page_size;
         const int page = (block < a.table_cols) ? a.page_table[(size_t)seq * a.table_cols + block] : -1;
         if (page < 0 || page >= a.num_pages) {
-            if (threadIdx.x == 0) atomicExch(a.error_flag, 1);
+            if (lane == 0) atomicExch(a.error_flag, 1);
         } else {
             kbase = (T*)a.cache + (((size_t)page * 2) * a.nkh * a.page_size + off) * a.hd;
         }
     }
     const size_t plane = (size_t)a.nkh * a.page_size * a.hd, head_step = (size_t)a.page_size * a.hd;
-    const int heads = a.nqh + (a.value_is_key ? a.nkh : 2 * a.nkh);
     constexpr int NP = HEAD_NORM_MAX_HD / 64;             // pairs a lane
-    for (int head = warp; head < heads; head += HEAD_NORM_WARPS) {
+    {
         const bool is_q = head < a.nqh, is_k = !is_q && head < a.nqh + a.nkh;
         T* src = (T*)a.qk + (size_t)row * a.row_stride + (size_t)head * a.hd;
         T* kdst = nullptr;
@@ -505,7 +502,7 @@ head_norm_rope_kv_kernel(HeadNormRopeArgs a) {
             }
             ss = fmaf(x0[e], x0[e], fmaf(x1[e], x1[e], ss));
         }
-        if (!is_q && !is_k) continue;
+        if (!is_q && !is_k) return;
         const void* wv = is_q ? a.q_w : a.k_w;
         if (wv) {
             ss = warp_sum(ss);
@@ -522,9 +519,12 @@ head_norm_rope_kv_kernel(HeadNormRopeArgs a) {
             for (int e = 0; e < NP; ++e) {
                 const int p = lane + 32 * e;
                 if (p < half) {
+                    float sn, cs;
+                    sincosf((float)pos * a.inv_freq[p], &sn, &cs);
+                    sn *= a.amp; cs *= a.amp;
                     const float u = x0[e], v = x1[e];
-                    x0[e] = u * cs[p] - v * sn[p];
-                    x1[e] = v * cs[p] + u * sn[p];
+                    x0[e] = u * cs - v * sn;
+                    x1[e] = v * cs + u * sn;
                 }
             }
         } else if (half > 0) {
@@ -544,7 +544,10 @@ head_norm_rope_kv_kernel(HeadNormRopeArgs a) {
                     const int i = 2 * (lane + 32 * e) + b;
                     if (i < a.rope_dim) {
                         const int p = i < half ? i : i - half;
-                        const float y = i < half ? st[i] * cs[p] - st[i + half] * sn[p] : st[i] * cs[p] + st[i - half] * sn[p];
+                        float sn, cs;
+                        sincosf((float)pos * a.inv_freq[p], &sn, &cs);
+                        sn *= a.amp; cs *= a.amp;
+                        const float y = i < half ? st[i] * cs - st[i + half] * sn : st[i] * cs + st[i - half] * sn;
                         if (b) x1[e] = y; else x0[e] = y;
                     }
                 }
@@ -583,7 +586,10 @@ extern "C" int braid_head_norm_rope_kv(void* qk, long long row_stride, int dtype
     const int esize = dtype == BRAID_F32 ? 4 : 2;
     // pairs move as one word where every head starts on a pair's boundary, in the rows and in the cache
     const bool pairs = (hd % 2 == 0) && (row_stride % 2 == 0) && (((uintptr_t)qk | (uintptr_t)cache) % (2 * esize) == 0);
-    const dim3 grid(rows), block(HEAD_NORM_WARPS * 32);
+    const int n_heads = nqh + (value_is_key ? nkh : 2 * nkh);
+    const long long blocks = (long long)rows * ((n_heads + HEAD_NORM_WARPS - 1) / HEAD_NORM_WARPS);
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("head_norm_rope_kv: %lld (row, head) pairs exceed one launch", (long long)rows * n_heads);
+    const dim3 grid((unsigned)blocks), block(HEAD_NORM_WARPS * 32);
     if (dtype == BRAID_F32) {
         if (pairs) braid_launch(head_norm_rope_kv_kernel<float, true>, grid, block, 0, s, a);
         else braid_launch(head_norm_rope_kv_kernel<float, false>, grid, block, 0, s, a);

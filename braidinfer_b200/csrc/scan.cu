@@ -152,13 +152,46 @@ struct ScanArgs {
     // chunked walk (pass != 0): wbuf [seq][chunk][head][dk][dv], dbuf [seq][chunk][head]([dk])
     float* wbuf; float* dbuf;
     int pass, chunk, max_chunks;
+    int gate_is_decay;           // DECAY_CHANNEL: `gate` holds the decays themselves (braid_scan_decay), not their logits
 };
+
+// sigmoid(z)^(1 / tau) through log sigmoid(z) = min(z, 0) - log1p(exp(-|z|)): no overflow, full precision near one
+__device__ __forceinline__ float decay_of_logit(float z, float inv_tau) {
+    return expf((fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * inv_tau);
+}
+
+// z[r, c] <- sigmoid(z[r, c] + b[c])^(1 / tau) in place: the decays of a long step, computed once instead of by every
+// CTA that walks a tile of the head's value columns, in every pass.
+template <typename T>
+__global__ void scan_decay_kernel(float* __restrict__ z, long long stride, const T* __restrict__ b, long long total, int n, float inv_tau) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long r = i / n;
+    const int c = (int)(i - r * n);
+    z[r * stride + c] = decay_of_logit(z[r * stride + c] + to_f32(b[c]), inv_tau);
+}
+
+extern "C" int braid_scan_decay(float* z, long long stride, const void* bias, int dtype, int rows, int n, float inv_tau, void* stream) {
+    if (rows <= 0 || n <= 0) return BRAID_OK;
+    const long long total = (long long)rows * n;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("scan_decay: %lld elements exceed one launch", total);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32) braid_launch(scan_decay_kernel<float>, dim3((int)blocks), dim3(256), 0, s, z, stride, (const float*)bias, total, n, inv_tau);
+    else if (dtype == BRAID_BF16) braid_launch(scan_decay_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, z, stride, (const __nv_bfloat16*)bias, total, n, inv_tau);
+    else BRAID_REFUSE("scan_decay: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
 
 template <typename T, int MODE, int RG, int R>
 __global__ void __launch_bounds__(SCAN_THREADS)
 linear_scan_kernel(ScanArgs a) {
     constexpr int CV = SCAN_CV, CG = SCAN_THREADS / RG, DVT = CG * CV, DKP = RG * R;
+    constexpr int TB = DKP <= 128 ? SCAN_TB : SCAN_TB / 2;      // tokens a batch: what a thread holds of the next batch fits its registers
     static_assert(RG >= 2 && RG <= 16 && (R == 8 || R == 16), "two column groups and RG row groups share a warp");
+    static_assert((TB * DKP) % SCAN_THREADS == 0 && (TB * DVT) % SCAN_THREADS == 0, "a batch is a whole number of elements a thread");
     pdl_trigger();
     const int h = blockIdx.x, seq = blockIdx.y;
     const int n_dvt = (a.dv + DVT - 1) / DVT;
@@ -175,9 +208,9 @@ linear_scan_kernel(ScanArgs a) {
     const int g = h / (a.heads / a.groups);
     extern __shared__ __align__(16) float sm[];
     float* sq = sm;                                          // [TB][DKP]
-    float* sk = sq + SCAN_TB * DKP;
-    float* sv = sk + SCAN_TB * DKP;                          // [TB][DVT]
-    float* skap = sv + SCAN_TB * DVT;                        // [TB] step sizes, [TB] decays of the head
+    float* sk = sq + TB * DKP;
+    float* sv = sk + TB * DKP;                               // [TB][DVT]
+    float* skap = sv + TB * DVT;                             // [TB] step sizes, [TB] decays of the head (8 floats each)
     float* sah = skap + SCAN_TB;
     float* sa = sah + SCAN_TB;                               // [TB][DKP] decays per channel (DECAY_CHANNEL)
     float head_a = 0.f, head_bias = 0.f, head_skip = 0.f;
@@ -204,39 +237,59 @@ linear_scan_kernel(ScanArgs a) {
     float hprod = 1.f;
     const bool outputs = a.pass != 1;
 
-    for (int t0 = t_begin; t0 < t_end; t0 += SCAN_TB) {
-        const int nt = min(SCAN_TB, t_end - t0);
-        __syncthreads();                                    // the batch before has been read
-        for (int idx = tid; idx < nt * DKP; idx += SCAN_THREADS) {
+    // A batch of TB tokens is asked for from global memory while the batch before it is walked: its numbers wait in
+    // registers (as they came, in the run's type) and go to shared memory, converted, when the walk has left it.
+    constexpr int NQ = TB * DKP / SCAN_THREADS, NV = TB * DVT / SCAN_THREADS;
+    T pq[NQ], pk[NQ], pv[NV], pg = from_f32<T>(0.f);
+    float pa[MODE == DECAY_CHANNEL ? NQ : 1];
+    auto fetch = [&](int t0) {
+        const int nt = min(TB, t_end - t0);
+#pragma unroll
+        for (int u = 0; u < NQ; ++u) {
+            const int idx = tid + u * SCAN_THREADS;
             const int t = idx / DKP, i = idx - t * DKP;
             const size_t row = (size_t)(r0 + t0 + t);
-            float qv = 0.f, kv = 0.f, av = 0.f;
-            if (i < dk) {
-                qv = to_f32(((const T*)a.q)[row * a.q_stride + (size_t)g * dk + i]) * a.q_scale;
-                kv = to_f32(((const T*)a.k)[row * a.k_stride + (size_t)g * dk + i]);
-                if (MODE == DECAY_CHANNEL) {
-                    const float z = ((const float*)a.gate)[row * a.gate_stride + (size_t)h * dk + i] +
-                                    to_f32(((const T*)a.gate_bias)[(size_t)h * dk + i]);
-                    // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
-                    av = expf((fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * a.inv_tau);
-                }
-            }
-            sq[idx] = qv;
-            sk[idx] = kv;
-            if (MODE == DECAY_CHANNEL) sa[idx] = av;
+            const bool in = t < nt && i < dk;
+            pq[u] = in ? ((const T*)a.q)[row * a.q_stride + (size_t)g * dk + i] : from_f32<T>(0.f);
+            pk[u] = in ? ((const T*)a.k)[row * a.k_stride + (size_t)g * dk + i] : from_f32<T>(0.f);
+            if (MODE == DECAY_CHANNEL) pa[u] = in ? ((const float*)a.gate)[row * a.gate_stride + (size_t)h * dk + i] : 0.f;
         }
-        for (int idx = tid; idx < nt * DVT; idx += SCAN_THREADS) {
+#pragma unroll
+        for (int u = 0; u < NV; ++u) {
+            const int idx = tid + u * SCAN_THREADS;
             const int t = idx / DVT, jj = idx - t * DVT;
             const size_t row = (size_t)(r0 + t0 + t);
-            sv[idx] = (dvt * DVT + jj < dv) ? to_f32(((const T*)a.v)[row * a.v_stride + (size_t)h * dv + dvt * DVT + jj]) : 0.f;
+            pv[u] = (t < nt && dvt * DVT + jj < dv) ? ((const T*)a.v)[row * a.v_stride + (size_t)h * dv + dvt * DVT + jj] : from_f32<T>(0.f);
         }
+        if (MODE == DECAY_HEAD && tid < nt) pg = ((const T*)a.gate)[(size_t)(r0 + t0 + tid) * a.gate_stride + h];
+    };
+    fetch(t_begin);
+    for (int t0 = t_begin; t0 < t_end; t0 += TB) {
+        const int nt = min(TB, t_end - t0);
+        __syncthreads();                                    // the batch before has been read
+#pragma unroll
+        for (int u = 0; u < NQ; ++u) {
+            const int idx = tid + u * SCAN_THREADS;
+            sq[idx] = to_f32(pq[u]) * a.q_scale;
+            sk[idx] = to_f32(pk[u]);
+            if (MODE == DECAY_CHANNEL) {
+                float av = pa[u];
+                if (!a.gate_is_decay) {
+                    const int i = idx % DKP;
+                    av = i < dk ? decay_of_logit(av + to_f32(((const T*)a.gate_bias)[(size_t)h * dk + i]), a.inv_tau) : 0.f;
+                }
+                sa[idx] = av;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < NV; ++u) sv[tid + u * SCAN_THREADS] = to_f32(pv[u]);
         if (MODE == DECAY_HEAD && tid < nt) {
-            const size_t row = (size_t)(r0 + t0 + tid);
-            const float x = to_f32(((const T*)a.gate)[row * a.gate_stride + h]) + head_bias;
+            const float x = to_f32(pg) + head_bias;
             const float dt = x > 20.f ? x : log1pf(expf(x));           // softplus
             skap[tid] = dt;
             sah[tid] = expf(head_a * dt);
         }
+        if (t0 + TB < t_end) fetch(t0 + TB);
         __syncthreads();
         for (int t = 0; t < nt; ++t) {
             float qv[R], kv[R], av[R], vv[CV];
@@ -349,7 +402,7 @@ extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* 
                                  long long state_stride, long long state_offset, const int* q_start, const int* q_len,
                                  const int* slot_ids, int dtype, int mode, int n_seqs, int heads, int groups, int dk, int dv,
                                  float q_scale, float inv_tau, int max_q_len, int chunk, float* work, long long work_floats,
-                                 void* stream) {
+                                 int gate_is_decay, void* stream) {
     if (n_seqs <= 0) return BRAID_OK;
     if (heads <= 0 || groups <= 0 || heads % groups) BRAID_REFUSE("linear_scan: %d heads do not divide into %d groups", heads, groups);
     if (dk <= 0 || dk > SCAN_MAX_DK || dv <= 0) BRAID_REFUSE("linear_scan: key size %d must be in (0, %d], value size %d positive", dk, SCAN_MAX_DK, dv);
@@ -367,7 +420,7 @@ extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* 
     if (n_seqs > 65535 || (long long)n_dvt * max_chunks > 65535) BRAID_REFUSE("linear_scan: the step exceeds the grid limits");
     ScanArgs a{q, q_stride, k, k_stride, v, v_stride, gate, gate_stride, gate_bias, a_log, skip, out, out_stride,
                (uint8_t*)state, state_stride, state_offset, q_start, q_len, slot_ids, heads, groups, dk, dv, q_scale, inv_tau,
-               nullptr, nullptr, 0, chunk, max_chunks};
+               nullptr, nullptr, 0, chunk, max_chunks, gate_is_decay};
     if (chunked) {
         a.wbuf = work;
         a.dbuf = work + (long long)n_seqs * max_chunks * heads * dk * dv;

@@ -30,6 +30,8 @@ class GatedLinearAttention(Mixer):
     (default 1), gate_rank (the inner size of the decay's low-rank map), and the tensor names q, k, v, g, a1, a2,
     a2_bias, norm, o (under the prefix)."""
 
+    DECAY_IN_PLACE_ROWS = 64
+
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
         p = params
@@ -91,8 +93,13 @@ class GatedLinearAttention(Mixer):
             a1 = a1.contiguous()                                        # the tensor-core product wants aligned rows
         z = self.a2.forward(a1, out_dtype=torch.float32)                # the decay's logit, before its bias
         o = torch.empty((rows, H * dv), dtype=torch.float32, device=x.device)
+        # in a long step every decay is read by many CTAs of the recurrence: computed once, in place; a short
+        # step computes them where they are used and saves the launch
+        ready = rows > self.DECAY_IN_PLACE_ROWS
+        if ready:
+            K.scan_decay(z, self.a2_bias, 1.0 / self.tau)
         K.linear_scan(q, k, v, z, self.a2_bias, o, state, 0, ctx, H, H, dk, dv, "channel",
-                      q_scale=dk ** -0.5, inv_tau=1.0 / self.tau)
+                      q_scale=dk ** -0.5, inv_tau=1.0 / self.tau, gate_is_decay=ready)
         padded = ctx.rows > ctx.n_tokens
         y = torch.zeros((rows, H * dv), dtype=x.dtype, device=x.device) if padded else self.rt.empty(rows, H * dv)
         K.gated_norm(o, g, self.norm_w, y, ctx.token_seq, dv, False, self.eps, out_scale=self.out_mult)

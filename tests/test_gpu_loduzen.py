@@ -340,8 +340,12 @@ def test_recurrence_whole_in_portions_and_token_by_token(K, dtype, mode, heads, 
             q, k, v, gate = cat(0), cat(1), cat(2), cat(3)
             out = torch.zeros(t.rows, heads * dv, dtype=torch.float32, device="cuda")
             if mode == "channel":
+                ready = chunk == 16                    # the decays computed once, in place, before the walk
+                if ready:
+                    gate = gate.clone()
+                    K.scan_decay(gate, bias, 1 / tau)
                 K.linear_scan(q[:, :groups * dk], k, v[:, :heads * dv], gate, bias, out, state, offset, t, heads, groups, dk, dv,
-                              "channel", q_scale=dk ** -0.5, inv_tau=1 / tau, chunk=chunk)
+                              "channel", q_scale=dk ** -0.5, inv_tau=1 / tau, chunk=chunk, gate_is_decay=ready)
             else:
                 K.linear_scan(q[:, :groups * dk], k, v[:, :heads * dv], gate[:, :heads], bias, out, state, offset, t, heads, groups,
                               dk, dv, "head", a_log=a_log, skip=skip, chunk=chunk)
