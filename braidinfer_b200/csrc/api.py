@@ -8,6 +8,7 @@ library, `get_kernels()` raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_longlong, c_float, c_void_p, c_char_p
 from typing import List, Optional
 
@@ -64,7 +65,11 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 PAIR_TOKEN_TILE = 256        # the token tile of the kernel that runs on pairs of SMs
-SCAN_CHUNK = 64              # tokens a chunk of a long prompt's recurrence (csrc/scan.cu); shorter steps walk in one pass
+# Tokens a chunk of a long prompt's recurrence (csrc/scan.cu): 128 for sequences of 1,024 tokens and more, 64 below
+# (2,048 tokens, 8 heads of 128 x 256: 0.42 / 0.32 / 0.29 / 0.30 ms with chunks of 32 / 64 / 128 / 256); steps whose
+# longest sequence brings less than two chunks walk in one pass.  BRAIDINFER_SCAN_CHUNK names one length for all
+# (0: never in chunks), for measurements.
+SCAN_CHUNK = int(os.environ["BRAIDINFER_SCAN_CHUNK"]) if os.environ.get("BRAIDINFER_SCAN_CHUNK") else None
 
 
 class RowScale:
@@ -780,7 +785,7 @@ class Kernels:
         dt = softplus(gate + gate_bias), a = exp(-exp(a_log) dt), kappa = dt (gate [rows, heads] in the run's
         type).  q, k [rows, groups * dk], v [rows, heads * dv] (views are fine); out float32 [rows, heads * dv].
         `gate_is_decay` (mode "channel"): `gate` holds the decays themselves, as `scan_decay` left them.
-        A step whose longest sequence brings at least two chunks of `chunk` tokens (default SCAN_CHUNK; 0: never)
+        A step whose longest sequence brings at least two chunks of `chunk` tokens (default: see SCAN_CHUNK; 0: never)
         walks its chunks side by side in three passes (see csrc/scan.cu); the results differ from the walk
         token by token by rounding only."""
         lib = self.part_library("scan")
@@ -797,7 +802,9 @@ class Kernels:
                                   "of the rows' element type")
         else:
             raise KernelError(f"linear_scan: unknown decay mode {mode!r}")
-        chunk = SCAN_CHUNK if chunk is None else int(chunk)
+        if chunk is None:
+            chunk = SCAN_CHUNK if SCAN_CHUNK is not None else (128 if int(ctx.max_q_len) >= 1024 else 64)
+        chunk = int(chunk)
         code = 0 if mode == "channel" else 1
         need = lib.braid_linear_scan_work_floats(ctx.n_seqs, int(ctx.max_q_len), chunk, heads, dk, dv, code)
         work = torch.empty(need, dtype=torch.float32, device=out.device) if need > 0 else None

@@ -571,6 +571,101 @@ head_norm_rope_kv_kernel(HeadNormRopeArgs a) {
     }
 }
 
+// The same for neighbouring pairs (or no rotation) with 16 bytes a lane: LPH lanes a head (LPH x 16 bytes hold the
+// head), so a warp takes 32 / LPH heads of a row.  For head sizes and strides that allow aligned 16-byte moves.
+template <typename T, int LPH>
+__global__ void __launch_bounds__(128)
+head_norm_rope_kv_vec_kernel(HeadNormRopeArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int VEC = 16 / sizeof(T), HPC = 128 / LPH;
+    const int sub = threadIdx.x / LPH, l = threadIdx.x % LPH;
+    const int heads = a.nqh + (a.value_is_key ? a.nkh : 2 * a.nkh);
+    const int per_row = (heads + HPC - 1) / HPC;
+    const int row = blockIdx.x / per_row;
+    const int head = (blockIdx.x - row * per_row) * HPC + sub;
+    const int seq = a.token_seq[row];
+    if (seq < 0) return;                                   // the whole CTA: one row
+    const int pos = a.positions[row];
+    const int i0 = l * VEC;
+    const bool in = head < heads && i0 < a.hd;             // lanes that hold nothing still take part in the shuffles
+    const bool is_q = head < a.nqh, is_k = !is_q && head < a.nqh + a.nkh;
+    T* src = (T*)a.qk + (size_t)row * a.row_stride + (size_t)head * a.hd + i0;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (in && !is_q && a.cache) {
+        const int block = pos / a.page_size, off = pos - block * a.page_size;
+        const int page = (block < a.table_cols) ? a.page_table[(size_t)seq * a.table_cols + block] : -1;
+        if (page < 0 || page >= a.num_pages) {
+            if (l == 0) atomicExch(a.error_flag, 1);
+        } else {
+            const int kvh = is_k ? head - a.nqh : head - a.nqh - a.nkh;
+            T* kplane = (T*)a.cache + ((((size_t)page * 2) * a.nkh + kvh) * a.page_size + off) * a.hd + i0;
+            T* vplane = kplane + (size_t)a.nkh * a.page_size * a.hd;
+            if (is_k) { kdst = kplane; if (a.value_is_key) vdst = vplane; }
+            else vdst = vplane;
+        }
+    }
+    T raw[VEC];
+    float x[VEC];
+    if (in) *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(src);
+    if (vdst) *reinterpret_cast<uint4*>(vdst) = *reinterpret_cast<const uint4*>(raw);
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+        x[e] = in ? to_f32(raw[e]) : 0.f;
+        ss = fmaf(x[e], x[e], ss);
+    }
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!in || (!is_q && !is_k)) return;
+    const void* wv = is_q ? a.q_w : a.k_w;
+    if (wv) {
+        const float r = 1.f / sqrtf(ss / (float)a.hd + a.eps);
+        T w[VEC];
+        *reinterpret_cast<uint4*>(w) = *reinterpret_cast<const uint4*>((const T*)wv + i0);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x[e] = x[e] * r * to_f32(w[e]);
+    }
+    const int half = a.rope_dim / 2;
+#pragma unroll
+    for (int e = 0; e < VEC; e += 2) {
+        const int p = (i0 + e) >> 1;
+        if (p < half) {
+            float sn, cs;
+            sincosf((float)pos * a.inv_freq[p], &sn, &cs);
+            sn *= a.amp; cs *= a.amp;
+            const float u = x[e], v = x[e + 1];
+            x[e] = u * cs - v * sn;
+            x[e + 1] = v * cs + u * sn;
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) raw[e] = from_f32<T>(x[e]);
+    *reinterpret_cast<uint4*>(src) = *reinterpret_cast<const uint4*>(raw);
+    if (kdst) *reinterpret_cast<uint4*>(kdst) = *reinterpret_cast<const uint4*>(raw);
+}
+
+template <typename T>
+static bool launch_head_norm_vec(const HeadNormRopeArgs& a, int heads, cudaStream_t s) {
+    constexpr int VEC = 16 / sizeof(T);
+    const int lanes = (a.hd + VEC - 1) / VEC;
+#define HN_LAUNCH(LPH)                                                                                        \
+    do {                                                                                                      \
+        const int hpc = 128 / LPH;                                                                            \
+        const long long blocks = (long long)a.rows * ((heads + hpc - 1) / hpc);                               \
+        if (blocks > 0x7fffffffLL) return false;                                                              \
+        braid_launch(head_norm_rope_kv_vec_kernel<T, LPH>, dim3((unsigned)blocks), dim3(128), 0, s, a);       \
+        return true;                                                                                          \
+    } while (0)
+    if (lanes <= 4) HN_LAUNCH(4);
+    if (lanes <= 8) HN_LAUNCH(8);
+    if (lanes <= 16) HN_LAUNCH(16);
+    if (lanes <= 32) HN_LAUNCH(32);
+#undef HN_LAUNCH
+    return false;
+}
+
 extern "C" int braid_head_norm_rope_kv(void* qk, long long row_stride, int dtype, const void* q_w, const void* k_w,
                                        const float* inv_freq, const int* positions, const int* token_seq,
                                        const int* page_table, void* cache, int rows, int nqh, int nkh, int hd,
@@ -587,6 +682,14 @@ extern "C" int braid_head_norm_rope_kv(void* qk, long long row_stride, int dtype
     // pairs move as one word where every head starts on a pair's boundary, in the rows and in the cache
     const bool pairs = (hd % 2 == 0) && (row_stride % 2 == 0) && (((uintptr_t)qk | (uintptr_t)cache) % (2 * esize) == 0);
     const int n_heads = nqh + (value_is_key ? nkh : 2 * nkh);
+    const int vec = 16 / esize;
+    // 16 bytes a lane where the heads, the rows, the norm weights and the cache allow aligned moves and pairs are neighbours
+    const bool wide = (adjacent || rope_dim == 0) && hd % vec == 0 && row_stride % vec == 0 &&
+                      (((uintptr_t)qk | (uintptr_t)cache | (uintptr_t)q_w | (uintptr_t)k_w) & 15) == 0;
+    if (wide && (dtype == BRAID_F32 || dtype == BRAID_BF16)) {
+        const bool done = dtype == BRAID_F32 ? launch_head_norm_vec<float>(a, n_heads, s) : launch_head_norm_vec<__nv_bfloat16>(a, n_heads, s);
+        if (done) BRAID_LAUNCH_CHECK();
+    }
     const long long blocks = (long long)rows * ((n_heads + HEAD_NORM_WARPS - 1) / HEAD_NORM_WARPS);
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("head_norm_rope_kv: %lld (row, head) pairs exceed one launch", (long long)rows * n_heads);
     const dim3 grid((unsigned)blocks), block(HEAD_NORM_WARPS * 32);

@@ -255,10 +255,11 @@ def test_attention_with_a_sink_and_a_factor_on_its_result(K, kernel, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("taps", [1, 2, 4])
-def test_causal_convolution_in_steps_of_any_size_with_slots_used_again(K, dtype, taps):
+@pytest.mark.parametrize("taps, C, stride, first", [(1, 21, 40, 3), (2, 21, 40, 3), (4, 21, 40, 3), (4, 48, 64, 8), (3, 16, 16, 0)])
+def test_causal_convolution_in_steps_of_any_size_with_slots_used_again(K, dtype, taps, C, stride, first):
+    """The last two cases allow aligned 16-byte loads and take the kernel that moves neighbouring channels together."""
     g = torch.Generator().manual_seed(taps)
-    C, stride, offset = 21, 40, 16
+    offset = 16
     w = dev(torch.randn(C, taps, generator=g), dtype)
     b = dev(torch.randn(C, generator=g), dtype)
     state_bytes = offset + (taps - 1) * C * 4 + 8
@@ -266,14 +267,14 @@ def test_causal_convolution_in_steps_of_any_size_with_slots_used_again(K, dtype,
     for round_ in range(2):                                                 # the second round uses the slots again
         state[[2, 0]] = 0                                                   # as the cache manager does when a slot is taken
         xs = [dev(torch.randn(n, stride, generator=g), dtype) for n in (23, 9)]
-        want = [P.silu(P.causal_conv(back(x)[:, 3:3 + C], back(w), back(b))) for x in xs]
+        want = [P.silu(P.causal_conv(back(x)[:, first:first + C], back(w), back(b))) for x in xs]
         at = [0, 0]
         for cut in ([1, 2], [2, 1], [3, 1], [1, 0], [9, 5], [7, 0]):        # 0: the sequence sits this step out
             live = [i for i in range(2) if cut[i]]
             rows = torch.cat([xs[i][at[i]:at[i] + cut[i]] for i in live] + [torch.zeros(1, stride, dtype=TORCH[dtype], device="cuda")])
             t = step_tables([cut[i] for i in live], slots=[[2, 0][i] for i in live], pad=1)
             y = torch.zeros(t.rows, C, dtype=TORCH[dtype], device="cuda")
-            K.causal_conv(rows[:, 3:3 + C], y, w, b, state, offset, t, silu=True)
+            K.causal_conv(rows[:, first:first + C], y, w, b, state, offset, t, silu=True)
             r = 0
             for i in live:
                 assert rel(y[r:r + cut[i]], want[i][at[i]:at[i] + cut[i]]) < (2e-6 if dtype == "float32" else 1e-2), (round_, cut, i)
@@ -361,7 +362,7 @@ def test_recurrence_whole_in_portions_and_token_by_token(K, dtype, mode, heads, 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("gate_first, width, group, per_column", [(False, 120, 40, False), (True, 96, 48, True), (True, 35, 35, True),
-                                                                  (False, 64, 8, False)])
+                                                                  (False, 64, 8, False), (True, 600, 300, True), (False, 516, 258, False)])
 def test_gated_norm_in_both_orders(K, dtype, gate_first, width, group, per_column):
     g = torch.Generator().manual_seed(width)
     rows = 9
