@@ -99,8 +99,10 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     from ..cache import PAGE_SIZE
     from .engine import Engine
     # every live request may leave its last page part empty: a page of slack for each request there can be
-    slack = PAGE_SIZE * max(1, min(512, a.max_tokens))
-    engine = Engine.from_folder(a.model, dtype=a.dtype, max_tokens=a.max_tokens + slack, verbose=True)
+    live = max(1, min(512, a.max_tokens))
+    slack = PAGE_SIZE * live
+    # as many sequence slots as there can be live requests: a model with recurrent mixers keeps a state area a slot
+    engine = Engine.from_folder(a.model, dtype=a.dtype, max_tokens=a.max_tokens + slack, max_slots=live, verbose=True)
 
     def say(msg: str) -> None:
         sys.stdout.write(msg + "\n")
