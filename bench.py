@@ -901,8 +901,8 @@ LODUZEN_SIZES = {
 def loduzen_config(z):
     left = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
             "mask": {"size": z["window"]},
-            "rot": {"base": 500000.0, "dims": z["dim"] // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
-    right = {"heads": z["lheads"], "dim": z["ldk"], "vdim": z["ldv"], "tau": 16.0}
+            "rot": {"base": 1e6, "dims": z["dim"] // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
+    right = {"heads": z["lheads"], "dim": z["ldk"], "vdim": z["ldv"], "tau": 8.0}
     par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0},
            "mlp": {"kind": "dense", "ff": z["ff"]}}
     ssm = {"type": "mamba2", "mixer": {"heads": z["sheads"], "vdim": z["sp"], "state": z["sn"], "groups": z["sg"], "conv": 4,
@@ -916,7 +916,7 @@ def loduzen_twin_config(z):
     return {"architectures": ["MistralForCausalLM"], "model_type": "mistral", "torch_dtype": "bfloat16",
             "num_hidden_layers": z["layers"], "hidden_size": z["width"], "num_attention_heads": z["heads"],
             "num_key_value_heads": z["kv"], "head_dim": z["dim"], "intermediate_size": z["ff"], "vocab_size": z["vocab"],
-            "rope_theta": 500000.0, "rms_norm_eps": 1e-6, "sliding_window": z["window"], "tie_word_embeddings": True,
+            "rope_theta": 1e6, "rms_norm_eps": 1e-6, "sliding_window": z["window"], "tie_word_embeddings": True,
             "max_position_embeddings": 32768}
 
 
@@ -1080,7 +1080,7 @@ def loduzen_kernels(z, T, B, C, timed, frac):
                 gate = torch.rand(rows, heads * dk, device=dev) * 0.1 + 0.9     # the decays themselves in a long step
                 bias = torch.zeros(heads * dk, device=dev, dtype=bf)
                 fn = lambda: K.linear_scan(qq, kk, vv, gate, bias, oo, state, 0, stp, heads, groups, dk, dv, "channel",
-                                           q_scale=dk ** -0.5, inv_tau=1 / 16, gate_is_decay=rows > 64)
+                                           q_scale=dk ** -0.5, inv_tau=1 / 8, gate_is_decay=rows > 64)
                 gbytes = rows * heads * dk * 4
             else:
                 gate = torch.randn(rows, heads, device=dev, dtype=bf)

@@ -13,7 +13,7 @@ config.json keys (nested objects; every size and every constant that differs bet
     layers[i].mlp           null, or kind "dense" with ff
 The inner size of the linear attention's decay map is given by a tensor's shape only (`l<i>.mix.right.a1` is
 [gate_rank, width]): `sizes_from_shapes` writes it into the optional key `layers[i].mixer.right.gate_rank`
-when a model folder is opened; without a folder (random weights) the key, or 16, is taken.
+when a model folder is opened; without a folder (random weights) the key, or 32, is taken.
 A key that is missing, or a value that no part here computes, is a `ConfigError` naming key and value.
 """
 from __future__ import annotations
@@ -26,7 +26,7 @@ from .errors import ConfigError
 
 MIXER_TYPES = ("parallel", "mamba2")
 MLP_KINDS = ("dense",)
-DEFAULT_GATE_RANK = 16
+DEFAULT_GATE_RANK = 32
 
 
 @dataclass(frozen=True)

@@ -50,7 +50,7 @@ LZ_B: Dict = {
     "architecture": "Loduzen", "vocab": 257, "width": 100, "norm": {"eps": 1e-5}, "token_side": {"dim": 12},
     "layers": [
         {"type": "mamba2", "mixer": _ssm(3, 20, 24, 1, 2, 1), "mlp": {"kind": "dense", "ff": 60}},
-        {"type": "parallel", "mixer": _par(_left(1, 1, 40, 1000, 500000.0, 20, 0.2), (5, 12, 20, 2.0), 1.0, 1.0),
+        {"type": "parallel", "mixer": _par(_left(1, 1, 40, 1000, 250000.0, 20, 0.2), (5, 12, 20, 2.0), 1.0, 1.0),
          "mlp": {"kind": "dense", "ff": 44}},
     ],
 }

@@ -61,7 +61,7 @@ def test_recipe_names_the_tensors_of_the_design_and_the_parts_beside_the_existin
     assert not any(n.startswith("l2.mlp") or n.startswith("l2.norm2") or ".left.v" in n for n in names)
     specs = tensor_specs_of(spec)
     assert specs["side.embed"].shape == (311, 24) and specs["l1.mix.in"].shape == (2 * 96 + 2 * 2 * 16 + 4, 96)
-    assert specs["l1.mix.conv"].shape == (96 + 64, 4) and specs["l0.mix.right.a2"].shape == (48, 16)
+    assert specs["l1.mix.conv"].shape == (96 + 64, 4) and specs["l0.mix.right.a2"].shape == (48, 32)
     assert [l.mixer.kind for l in spec.layers] == ["parallel", "mamba2", "parallel"]
     assert spec.layers[0].mixer.params["left"].kind == "gqa_attention" and spec.layers[0].layer_input.kind == "gated_token_table"
     assert spec_of(LZ_C).layers[0].layer_input is None
