@@ -57,7 +57,8 @@ causal_conv_kernel(ConvArgs a) {
     ((T*)a.y)[(size_t)row * a.y_stride + c] = from_f32<T>(acc);
 }
 
-// The same with 16 bytes of neighbouring channels a thread (8 bfloat16 or 4 float32 numbers): for rows and channel
+#define CONV_ROWS_PER_THREAD 4
+// The same with 16 bytes of neighbouring channels and four neighbouring rows a thread (8 bfloat16 or 4 float32 numbers): for rows and channel
 // counts that allow aligned loads.  The thread's weights (its channels' TAPS numbers each lie one after the other)
 // and biases come as 16-byte loads too: loaded one by one, lanes 64 bytes apart, they cost sixteen cache lines an
 // instruction and the kernel five times its time.
@@ -66,43 +67,53 @@ __global__ void __launch_bounds__(128)
 causal_conv_vec_kernel(ConvArgs a) {
     pdl_trigger();
     pdl_wait();
-    constexpr int VEC = 16 / sizeof(T);
+    constexpr int VEC = 16 / sizeof(T), RPT = CONV_ROWS_PER_THREAD, SPAN = RPT + TAPS - 1;
     const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
-    const int row = blockIdx.y;
+    const int row0 = blockIdx.y * RPT;
     if (c0 >= a.channels) return;
-    const int seq = a.token_seq[row];
-    if (seq < 0) return;
-    const int o = row - a.q_start[seq];
-    const float* st = (const float*)(a.state + (size_t)a.slot_ids[seq] * a.state_stride + a.state_offset);
     T wl[VEC * TAPS], bl[VEC];
 #pragma unroll
     for (int u = 0; u < TAPS; ++u)
         *reinterpret_cast<uint4*>(wl + u * VEC) = *reinterpret_cast<const uint4*>((const T*)a.w + (size_t)c0 * TAPS + u * VEC);
     if (a.b) *reinterpret_cast<uint4*>(bl) = *reinterpret_cast<const uint4*>((const T*)a.b + c0);
-    float acc[VEC];
+    // the RPT rows of this thread and the TAPS - 1 rows before them, loaded once: a row serves up to TAPS outputs
+    T xin[SPAN][VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) acc[e] = a.b ? to_f32(bl[e]) : 0.f;
-#pragma unroll
-    for (int j = 0; j < TAPS; ++j) {
-        const int back = TAPS - 1 - j;
-        float xv[VEC];
-        if (o - back >= 0) {
-            T raw[VEC];
-            *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>((const T*)a.x + (size_t)(row - back) * a.x_stride + c0);
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) xv[e] = to_f32(raw[e]);
-        } else {
-            const float* sp = st + (size_t)(TAPS - 1 + (o - back)) * a.channels + c0;
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) xv[e] = sp[e];
-        }
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) acc[e] = fmaf(to_f32(wl[e * TAPS + j]), xv[e], acc[e]);
+    for (int u = 0; u < SPAN; ++u) {
+        const int r = row0 - (TAPS - 1) + u;
+        if (r >= 0 && r < a.rows) *reinterpret_cast<uint4*>(xin[u]) = *reinterpret_cast<const uint4*>((const T*)a.x + (size_t)r * a.x_stride + c0);
     }
-    T out[VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) out[e] = from_f32<T>(a.silu ? silu_f32(acc[e]) : acc[e]);
-    *reinterpret_cast<uint4*>((T*)a.y + (size_t)row * a.y_stride + c0) = *reinterpret_cast<const uint4*>(out);
+    for (int rr = 0; rr < RPT; ++rr) {
+        const int row = row0 + rr;
+        if (row >= a.rows) break;
+        const int seq = a.token_seq[row];
+        if (seq < 0) continue;
+        const int o = row - a.q_start[seq];
+        const float* st = (const float*)(a.state + (size_t)a.slot_ids[seq] * a.state_stride + a.state_offset);
+        float acc[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] = a.b ? to_f32(bl[e]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+            const int back = TAPS - 1 - j;
+            float xv[VEC];
+            if (o - back >= 0) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) xv[e] = to_f32(xin[rr + j][e]);       // row - back = row0 - (TAPS - 1) + rr + j
+            } else {
+                const float* sp = st + (size_t)(TAPS - 1 + (o - back)) * a.channels + c0;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) xv[e] = sp[e];
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc[e] = fmaf(to_f32(wl[e * TAPS + j]), xv[e], acc[e]);
+        }
+        T out[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) out[e] = from_f32<T>(a.silu ? silu_f32(acc[e]) : acc[e]);
+        *reinterpret_cast<uint4*>((T*)a.y + (size_t)row * a.y_stride + c0) = *reinterpret_cast<const uint4*>(out);
+    }
 }
 
 // The state after the step: the sequence's last taps - 1 inputs.  One thread per (sequence, channel)
@@ -146,7 +157,7 @@ extern "C" int braid_causal_conv(const void* x, long long x_stride, void* y, lon
     const int vec = dtype == BRAID_F32 ? 4 : 8;
     const bool wide = taps >= 2 && taps <= 4 && channels % vec == 0 && x_stride % vec == 0 && y_stride % vec == 0 &&
                       (((uintptr_t)x | (uintptr_t)y | (uintptr_t)w | (uintptr_t)b) & 15) == 0;
-    const dim3 gv((channels / vec + 127) / 128, rows);
+    const dim3 gv((channels / vec + 127) / 128, (rows + CONV_ROWS_PER_THREAD - 1) / CONV_ROWS_PER_THREAD);
 #define CONV_LAUNCH(TT)                                                                                       \
     do {                                                                                                      \
         if (wide && taps == 2) braid_launch(causal_conv_vec_kernel<TT, 2>, gv, dim3(128), 0, s, a);           \
