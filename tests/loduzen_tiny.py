@@ -107,6 +107,39 @@ def make_loduzen_folder(tmp_path, name: str, cfg: Dict = None, seed: int = None)
     return folder
 
 
+def random_config(seed: int) -> Dict:
+    """A configuration drawn from a seed: sizes, head counts, the order and number of layers, windows and constants
+    all vary, within what a test can afford."""
+    import random
+    r = random.Random(seed)
+
+    def divisor(n):
+        return r.choice([d for d in range(1, n + 1) if n % d == 0])
+
+    layers = []
+    for _ in range(r.randint(2, 5)):
+        mlp = {"kind": "dense", "ff": r.choice([24, 40, 56, 72, 100])} if r.random() < 0.8 else None
+        if r.random() < 0.6:
+            heads = r.choice([1, 2, 3, 4, 6, 8])
+            dim = r.choice([8, 16, 24, 32, 48, 64, 80, 128])
+            dims = 2 * r.randint(0, dim // 2)
+            scaling = (r.choice([1.5, 2.0, 4.0, 8.0]), r.choice([16, 32, 64, 256]), r.choice([8.0, 16.0, 32.0]), r.choice([1.0, 2.0])) \
+                if r.random() < 0.7 else None
+            left = _left(heads, divisor(heads), dim, r.choice([1, 2, 5, 17, 33, 64, 65, 100, 500]), r.choice([100.0, 1e4, 1e6]), dims,
+                         r.choice([dim ** -0.5, 0.2, 0.07]), scaling)
+            right = (r.randint(1, 5), r.choice([4, 8, 12, 20, 32, 40, 72]), r.choice([4, 8, 12, 24, 36, 48]), r.choice([1.0, 2.0, 8.0, 32.0]))
+            layers.append({"type": "parallel", "mixer": _par(left, right, r.choice([0.5, 1.0, 1.3]), r.choice([0.7, 1.0, 1.6])), "mlp": mlp})
+        else:
+            heads, vdim = r.choice([1, 2, 4, 6, 8]), r.choice([4, 8, 12, 16, 24, 40])
+            layers.append({"type": "mamba2", "mixer": _ssm(heads, vdim, r.choice([4, 8, 16, 24, 48, 64, 80]), divisor(heads), r.randint(1, 5),
+                                                            divisor(heads * vdim) if r.random() < 0.5 else divisor(heads)), "mlp": mlp})
+    cfg = {"architecture": "Loduzen", "vocab": r.randint(90, 400), "width": r.choice([40, 48, 64, 72, 96, 100]),
+           "norm": {"eps": r.choice([1e-6, 1e-5])}, "layers": layers}
+    if r.random() < 0.7:
+        cfg["token_side"] = {"dim": r.choice([4, 8, 12, 16, 24])}
+    return cfg
+
+
 def folder_config(folder: str) -> Dict:
     with open(os.path.join(folder, "config.json")) as f:
         return json.load(f)

@@ -13,7 +13,7 @@ import pytest
 import torch
 
 import plain_loduzen as P
-from loduzen_tiny import LZ_CONFIGS, folder_config, make_loduzen_folder
+from loduzen_tiny import LZ_CONFIGS, folder_config, make_loduzen_folder, random_config
 from tiny import random_prompts, read_weights
 
 pytestmark = pytest.mark.gpu
@@ -191,12 +191,12 @@ def plain_attention(q, keys, values, pos, kv_len, window, scale, sink, nkh):
     return out
 
 
-@pytest.mark.parametrize("kernel", ["simple_f32", "simple_bf16", "mma_prompt", "mma_few_1", "mma_few_9", "tcgen05_prompt"])
+@pytest.mark.parametrize("kernel", ["simple_f32", "simple_bf16", "mma_prompt", "mma_few_1", "mma_few_9", "tcgen05_prompt", "tcgen05_prompt_128"])
 @pytest.mark.parametrize("window", [0, 70, 1])
 def test_attention_with_a_sink_and_a_factor_on_its_result(K, kernel, window):
     g = torch.Generator().manual_seed(window + len(kernel))
     dtype = "float32" if kernel == "simple_f32" else "bfloat16"
-    nqh, nkh, hd, page, scale, factor = 4, 2, 64 if kernel == "tcgen05_prompt" else 32, 64, 0.35, 1.3
+    nqh, nkh, hd, page, scale, factor = 4, 2, {"tcgen05_prompt": 64, "tcgen05_prompt_128": 128}.get(kernel, 32), 64, 0.35, 1.3
     few = kernel.startswith("mma_few")
     lengths, before = ([1, 2], [700, 130]) if few else ([150, 37], [0, 200])
     t = step_tables(lengths, before, pad=1)
@@ -234,7 +234,7 @@ def test_attention_with_a_sink_and_a_factor_on_its_result(K, kernel, window):
         if kernel.startswith("simple"):
             K.attn_simple(q, out, cache, table, t.positions, t.token_seq, nqh, nkh, hd, page, window or None, scale, sink=sink,
                           out_scale=factor)
-        elif kernel == "tcgen05_prompt":
+        elif kernel.startswith("tcgen05_prompt"):
             K.attn_tc(q, out, cache, table, t.q_start, t.q_len, t.kv_before, 2, max(lengths), nqh, nkh, hd, window or None, scale,
                       sink=sink, out_scale=factor)
         else:
@@ -582,6 +582,30 @@ def test_no_window_on_the_attention_through_a_hand_made_description(folders, ora
         at += c
     tally.close()
     assert eng.cache.pages_in_use() == [6, 6]
+    eng.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_configurations_drawn_from_a_seed(tmp_path, seed, dtype):
+    """Other sizes, head counts, layer orders, windows and constants than any written by hand: a prompt in two
+    portions beside a second request, then both decoded together, against the plain implementation."""
+    cfg = random_config(seed)
+    folder = make_loduzen_folder(tmp_path, f"r{seed}", cfg=cfg, seed=100 + seed)
+    oracle = Oracle(folder)
+    eng = engine(folder, dtype, max_tokens=64 * 8, max_slots=3)
+    a, b = random_prompts(cfg["vocab"], [150, 21], seed)
+    wa, wb = oracle.logits(a), oracle.logits(b)
+    sa, sb, tally = eng.open(), eng.open(), Tally(dtype)
+    tally.add(eng.step([(sa, a[:3])], want="all"), wa[:3], "first tokens")
+    lg = eng.step([(sa, a[3:135]), (sb, b[:9])], want="all")
+    tally.add(lg[:132], wa[3:135], "portion")
+    tally.add(lg[132:], wb[:9], "beside it")
+    for t in range(12):
+        lg = eng.step([(sa, [a[135 + t]]), (sb, [b[9 + t]])], want="last")
+        tally.add(lg[:1], wa[135 + t:136 + t], ("decoded", t))
+        tally.add(lg[1:], wb[9 + t:10 + t], ("decoded beside", t))
+    tally.close()
     eng.check()
 
 
